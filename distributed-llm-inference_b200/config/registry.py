@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration and model.
 
-The name is ``config.json["architectures"][0]``; a file without that key is
-looked up by ``model_type``.  (The reference has no registry: it keys on
+The name is ``config.json["architectures"][0]`` (or the single name under
+``"architecture"``); a file without either key is looked up by ``model_type``.  (The reference has no registry: it keys on
 ``model_type`` alone, src/dli/model/config.py:91-93.)
 """
 
@@ -13,6 +13,7 @@ from pathlib import Path
 from typing import Any, Callable
 
 from .llama import LlamaConfig, UnsupportedModelError, llama_model_spec
+from .pazenex import PazenexConfig, pazenex_model_spec
 from .spec import ModelSpec
 
 
@@ -36,11 +37,11 @@ def unregister_architecture(name: str) -> None:
 
 
 def resolve_architecture(cfg: dict[str, Any]) -> Architecture:
-    names = cfg.get("architectures") or []
+    names = cfg.get("architectures") or ([cfg["architecture"]] if cfg.get("architecture") else [])
     if names:
         if names[0] in _ARCHITECTURES:
             return _ARCHITECTURES[names[0]]
-        raise UnsupportedModelError(f"architectures[0]={names[0]!r} is not registered (known: {sorted(_ARCHITECTURES)})")
+        raise UnsupportedModelError(f"architecture {names[0]!r} is not registered (known: {sorted(_ARCHITECTURES)})")
     model_type = cfg.get("model_type")
     for arch in _ARCHITECTURES.values():
         if model_type in arch.model_types:
@@ -58,3 +59,4 @@ def load_config(model_dir: str | Path) -> tuple[Architecture, Any]:
 register_architecture(
     Architecture("LlamaForCausalLM", LlamaConfig.from_hf_dict, llama_model_spec, model_types=("llama",))
 )
+register_architecture(Architecture("Pazenex", PazenexConfig.from_dict, pazenex_model_spec))

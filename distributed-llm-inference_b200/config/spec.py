@@ -41,6 +41,9 @@ class RunStep:
 
     layer: int
     cache_of: int | None = None
+    # index into ``ModelSpec.entries``: a part that acts on the residual stream right before this entry's layer
+    # (what a looped span of layers adds to the stream at the start of a pass, for instance)
+    entry: int | None = None
 
 
 @dataclass(frozen=True)
@@ -52,9 +55,12 @@ class ModelSpec:
     run_order: tuple[RunStep, ...]
     final_norm: PartSpec
     head: PartSpec
+    entries: tuple[PartSpec, ...] = ()  # ``stream_entry`` parts that run steps name by index
 
     def __post_init__(self) -> None:
         for i, step in enumerate(self.run_order):
+            if step.entry is not None and not 0 <= step.entry < len(self.entries):
+                raise ValueError(f"run_order[{i}] names entry {step.entry}, model has {len(self.entries)}")
             if not 0 <= step.layer < len(self.layers):
                 raise ValueError(f"run_order[{i}] names layer {step.layer}, model has {len(self.layers)}")
             if step.cache_of is not None:

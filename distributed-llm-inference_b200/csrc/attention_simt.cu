@@ -13,7 +13,7 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
                                             const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                             const int* __restrict__ block_tables, int max_blocks,
                                             const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n,
-                                            int nh, int nkv, int d, int page_size, int window, float scale) {
+                                            int nh, int nkv, int d, int page_size, int window, float scale, float sink) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -67,6 +67,8 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
     }
     m = m_new;
   }
+  // a sink: one more term exp(sink) in the denominator that has no value (sink = -inf: none)
+  if (sink != -CUDART_INF_F) l += expf(sink - m);
   const float inv = 1.f / l;
   T* o = out + (size_t)t * nh * d + (size_t)h * d;
 #pragma unroll
@@ -79,7 +81,7 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
 DLI_EXPORT int dli_paged_attention_simt(void* out, const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                         const int* block_tables, int max_blocks, const int* seq_of_token,
                                         const int* positions, int n, int nh, int nkv, int d, int page_size, int window,
-                                        float scale, int dtype, cudaStream_t stream) {
+                                        float scale, float sink, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (d < 1 || d > 256 || nkv < 1 || nh % nkv) return DLI_ERR_UNSUPPORTED;
   const int warps = 4;
@@ -89,10 +91,10 @@ DLI_EXPORT int dli_paged_attention_simt(void* out, const void* q, int q_stride, 
   if (dtype == DLI_F32)
     launch_pdl((paged_attention_simt_kernel<float>), dim3(blocks), dim3(warps * 32), smem, stream, 1, 
         (float*)out, (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, block_tables, max_blocks,
-        seq_of_token, positions, n, nh, nkv, d, page_size, window, scale);
+        seq_of_token, positions, n, nh, nkv, d, page_size, window, scale, sink);
   else
     launch_pdl((paged_attention_simt_kernel<__nv_bfloat16>), dim3(blocks), dim3(warps * 32), smem, stream, 1, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-        block_tables, max_blocks, seq_of_token, positions, n, nh, nkv, d, page_size, window, scale);
+        block_tables, max_blocks, seq_of_token, positions, n, nh, nkv, d, page_size, window, scale, sink);
   return (int)cudaGetLastError();
 }

@@ -471,3 +471,59 @@ DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, 
     launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I, tiled);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- activation of a plain (ungated) feed-forward
+// x <- act(x) in place; kinds: 0 relu(x)^2, 1 gelu with the tanh approximation, 2 silu.
+#define DLI_ACT_RELU2 0
+#define DLI_ACT_GELU_TANH 1
+#define DLI_ACT_SILU 2
+
+__device__ __forceinline__ float apply_activation(float z, int kind) {
+  if (kind == DLI_ACT_RELU2) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  if (kind == DLI_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.f + expf(-z));
+}
+
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ x, size_t total, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = from_float<T>(apply_activation(to_float(x[i]), kind));
+}
+
+// bfloat16, total % 8 == 0: 16 bytes a thread
+__global__ void activation_bf16_vec_kernel(__nv_bfloat16* __restrict__ x, size_t units, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < units; i += (size_t)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x + i * 8, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = apply_activation(v[k], kind);
+    store8(x + i * 8, v);
+  }
+}
+
+DLI_EXPORT int dli_activation(void* x, long long total, int kind, int dtype, cudaStream_t stream) {
+  if (total == 0) return 0;
+  if (kind < 0 || kind > 2) return DLI_ERR_UNSUPPORTED;
+  const int threads = 256;
+  const size_t cap = (size_t)sm_count() * 16;
+  if (dtype == DLI_BF16 && total % 8 == 0 && ((uintptr_t)x % 16) == 0) {
+    const size_t units = (size_t)total / 8;
+    const size_t blocks = (units + threads - 1) / threads;
+    launch_pdl((activation_bf16_vec_kernel), dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(threads), 0, stream, 1, (__nv_bfloat16*)x, units, kind);
+    return (int)cudaGetLastError();
+  }
+  const size_t blocks = ((size_t)total + threads - 1) / threads;
+  const dim3 grid((unsigned)(blocks < cap ? blocks : cap));
+  if (dtype == DLI_F32)
+    launch_pdl((activation_kernel<float>), grid, dim3(threads), 0, stream, 1, (float*)x, (size_t)total, kind);
+  else
+    launch_pdl((activation_kernel<__nv_bfloat16>), grid, dim3(threads), 0, stream, 1, (__nv_bfloat16*)x, (size_t)total, kind);
+  return (int)cudaGetLastError();
+}

@@ -85,14 +85,15 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
 
 
 def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None,
-                    splits: int | None = None) -> None:
+                    splits: int | None = None, sink: float | None = None) -> None:
     """Attention of every token of the step over its sequence's pages.  ``splits``: key runs per single-token
-    sequence, if the caller fixed them (a recorded graph); otherwise chosen from this step's shape."""
+    sequence, if the caller fixed them (a recorded graph); otherwise chosen from this step's shape.  ``sink``: the
+    score of a term that is added to every softmax denominator and carries no value (None: no such term)."""
     group = batch.group(cache.group)
     _, nkv, _, d = cache.k.shape
     if out.dtype != torch.bfloat16 or not ops.mma_head_dim_supported(d):
         ops.paged_attention_simt(out, qkv, cache.k, cache.v, group.block_tables, batch.seq_of_token, batch.positions,
-                                 num_heads, scale, window)
+                                 num_heads, scale, window, sink)
         return
     singles, total = batch.num_single, batch.num_seqs
     if singles:
@@ -105,10 +106,10 @@ def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_head
                        torch.empty(rows * splits * 2, dtype=torch.float32, device=out.device))
         kernel = ops.paged_decode_tma if tma else ops.paged_attention_mma
         args = (out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, 0, singles) + (() if tma else (1,))
-        kernel(*args, 0, num_heads, scale, window, splits, scratch, *((batch.max_kv_len_single,) if tma else ()))
+        kernel(*args, 0, num_heads, scale, window, splits, scratch, *((batch.max_kv_len_single,) if tma else ()), sink=sink)
     if total > singles and ops.prefill_tc_supported(d, cache.page_size):
         ops.paged_prefill_tc(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles, total - singles,
-                             batch.max_q_len, num_heads, scale, window)
+                             batch.max_q_len, num_heads, scale, window, sink=sink)
     elif total > singles:
         ops.paged_attention_mma(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles,
-                                total - singles, batch.max_q_len, singles, num_heads, scale, window)
+                                total - singles, batch.max_q_len, singles, num_heads, scale, window, sink=sink)

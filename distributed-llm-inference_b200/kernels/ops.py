@@ -55,6 +55,12 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+def _sink(sink: float | None) -> float:
+    """The attention kernels' sink argument: the score of one more term of the softmax denominator that has no
+    value (exp(sink) is added to the sum of the exponentials), or -inf for none."""
+    return float("-inf") if sink is None else float(sink)
+
+
 def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
     if not t.is_cuda:
         raise KernelError(f"{name} must be a CUDA tensor: the engine has no CPU path")
@@ -235,8 +241,9 @@ def paged_attention_simt(
     num_heads: int,
     scale: float,
     window: int | None = None,
+    sink: float | None = None,
 ) -> None:
-    """Causal attention of every token over its sequence's pages, on CUDA cores.
+    """Causal attention of every token over its sequence's pages, on CUDA cores.  ``sink``: see ``_sink``.
 
     out [n, nh * d]; queries are the first nh * d columns of qkv; pools [pages, nkv, page_size, d];
     block_tables [seqs, max_blocks]; a token at position p reads keys max(0, p - window + 1) .. p.
@@ -252,11 +259,11 @@ def paged_attention_simt(
         raise KernelError(f"paged_attention_simt: head_dim {d} (<= 256) / heads {num_heads} per kv head {nkv} not supported")
     f = _fn(
         "attention_simt.cu", "dli_paged_attention_simt",
-        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_int, c_void_p],
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_float, c_int, c_void_p],
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1],
-          _ptr(seq_of_token), _ptr(positions), n, num_heads, nkv, d, page_size, int(window or 0), scale, DT_CODE[out.dtype], _stream()),
+          _ptr(seq_of_token), _ptr(positions), n, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), DT_CODE[out.dtype], _stream()),
         "paged_attention_simt",
     )
 
@@ -280,6 +287,7 @@ def paged_prefill_tc(
     scale: float,
     window: int | None = None,
     query_tiles: int = 0,
+    sink: float | None = None,
 ) -> None:
     """bfloat16 attention for prompt portions on tcgen05 tensor cores with TMA-fed pages
     (head size 64 or 128; page sizes 8, 16, 32, 64, 128).  Arguments as paged_attention_mma.
@@ -297,13 +305,13 @@ def paged_prefill_tc(
         raise KernelError("paged_prefill_tc: sequence range outside the batch")
     f = _fn(
         "attention_tc.cu", "dli_paged_prefill_tc",
-        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_int, c_void_p],
+        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_float, c_int, c_void_p],
     )
     if query_tiles not in (0, 1, 2):
         raise KernelError("paged_prefill_tc: query_tiles is 0 (choose), 1 or 2")
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
-          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, d, page_size, int(window or 0), scale, query_tiles, _stream()),
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), query_tiles, _stream()),
         "paged_prefill_tc",
     )
 
@@ -329,6 +337,7 @@ def paged_decode_tma(
     splits: int = 1,
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
     max_kv_len: int = 0,
+    sink: float | None = None,
 ) -> None:
     """bfloat16 attention of single-token sequences whose keys and values arrive by TMA (head size
     64 or 128; page sizes 8, 16, 32, ...).  Arguments as paged_attention_mma with max_q_len = 1.
@@ -356,11 +365,11 @@ def paged_decode_tma(
     f = _fn(
         "attention_tc.cu", "dli_paged_decode_tma",
         [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8
-        + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
+        + [c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
-          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, first_row, num_heads, nkv, d, page_size, int(window or 0), scale, splits,
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, first_row, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), splits,
           _ptr(acc), _ptr(ml), int(max_kv_len), _stream()),
         "paged_decode_tma",
     )
@@ -470,6 +479,7 @@ def paged_attention_mma(
     window: int | None = None,
     splits: int = 1,
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
+    sink: float | None = None,
 ) -> None:
     """bfloat16 tensor-core attention for the sequences [seq0, seq0 + num_seqs) of a batch.
 
@@ -501,13 +511,13 @@ def paged_attention_mma(
     f = _fn(
         "attention_mma.cu", "dli_paged_attention_mma",
         [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
-        + [c_int] * 8 + [c_float, c_int, c_void_p, c_void_p, c_void_p],
+        + [c_int] * 8 + [c_float, c_float, c_int, c_void_p, c_void_p, c_void_p],
         {"HEAD_DIM": d},
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1],
           _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, first_row, num_heads, nkv, page_size, int(window or 0),
-          scale, splits, _ptr(acc), _ptr(ml), _stream()),
+          scale, _sink(sink), splits, _ptr(acc), _ptr(ml), _stream()),
         "paged_attention_mma",
     )
     global launch_count
@@ -782,3 +792,195 @@ def dense_gemm_error() -> int:
 def skinny_gemm_error() -> int:
     """0, or which bounded wait of the decode matrix product ran out since the library was loaded."""
     return _fn("skinny_gemm.cu", "dli_skinny_gemm_error", [])()
+
+
+# ------------------------------------------------------------------ layer norm around the residual stream
+
+
+def post_add_layernorm(y: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor | None, w_post: torch.Tensor | None,
+                       w_pre: torch.Tensor | None, eps_post: float, eps_pre: float, rows: torch.Tensor | None = None) -> None:
+    """Layer norm (weight, no bias) on both sides of the residual addition, in one kernel:
+
+        v = h[s] + LN(a[s]) * w_post     (the addition is skipped when ``a`` is None)
+        y[r] = LN(v) * w_pre             (skipped when ``y`` is None)
+
+    with s = rows[r] (or r).  Without ``rows`` v is written back to ``h``.  LN(x) = (x - mean) / sqrt(var + eps),
+    var the mean of the squared deviations; all in float32."""
+    _need(h, "h", torch.float32)
+    n, H = h.shape
+    dtype = y.dtype if y is not None else (a.dtype if a is not None else None)
+    if dtype not in DT_CODE:
+        raise KernelError("post_add_layernorm: nothing to do, or a dtype that is not supported")
+    if a is not None:
+        _need(a, "a", dtype), _need(w_post, "w_post", torch.float32)
+        if a.shape != h.shape or w_post.numel() != H:
+            raise KernelError("post_add_layernorm: a and h differ in shape, or w_post is not [H]")
+    n_rows = n
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_rows = rows.numel()
+    if y is not None:
+        _need(y, "y"), _need(w_pre, "w_pre", torch.float32)
+        if tuple(y.shape) != (n_rows, H) or w_pre.numel() != H:
+            raise KernelError("post_add_layernorm: y must be [rows, H] and w_pre [H]")
+    f = _fn("layernorm.cu", "dli_post_add_layernorm",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(y), _ptr(h), _ptr(a), _ptr(w_post), _ptr(w_pre), _ptr(rows), n_rows, H, eps_post, eps_pre, DT_CODE[dtype], _stream()),
+           "post_add_layernorm")
+
+
+def stream_reinject(h: torch.Tensor, table: torch.Tensor | None, ids: torch.Tensor | None, vec: torch.Tensor | None) -> None:
+    """h[t] += table[ids[t]] + vec: the embedding of the step's tokens (if ``table``) and one vector (if ``vec``) are
+    added to the float32 residual stream."""
+    _need(h, "h", torch.float32)
+    n, H = h.shape
+    code = DT_CODE[torch.float32]
+    if table is not None:
+        _need(table, "table"), _need(ids, "ids", torch.int32)
+        if table.dtype not in DT_CODE or table.shape[1] != H or ids.numel() != n:
+            raise KernelError("stream_reinject: shapes or dtype do not agree")
+        code = DT_CODE[table.dtype]
+    if vec is not None:
+        _need(vec, "vec", torch.float32)
+        if vec.numel() != H:
+            raise KernelError("stream_reinject: vec must be [H]")
+    f = _fn("layernorm.cu", "dli_stream_reinject", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(table), _ptr(ids), _ptr(vec), n, H, code, _stream()), "stream_reinject")
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """x <- act(x) in place and returned: ``relu2`` (the square of relu), ``gelu_tanh``, ``silu``."""
+    _need(x, "x")
+    if x.dtype not in DT_CODE or kind not in ACTIVATIONS:
+        raise KernelError(f"activation: dtype {x.dtype} or kind {kind!r} (known: {sorted(ACTIVATIONS)}) not supported")
+    f = _fn("elementwise.cu", "dli_activation", [c_void_p, c_longlong, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.numel(), ACTIVATIONS[kind], DT_CODE[x.dtype], _stream()), "activation")
+    return x
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+# ------------------------------------------------------------------ between an attention mixer's projections and its kernel
+
+
+def qk_norm_rotary_store(proj: torch.Tensor, wq: torch.Tensor | None, wk: torch.Tensor | None, eps: float, positions: torch.Tensor,
+                         inv_freq: torch.Tensor | None, slots: torch.Tensor | None, k_pool: torch.Tensor | None,
+                         v_pool: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
+                         page_size: int, write_kv: bool = True, values_from_keys: bool = True) -> torch.Tensor:
+    """proj [n, >= (nh + nkv) d]: q | k (| v, when the values are not the keys) as projected.  With ``wq`` and ``wk``
+    q and k are each divided by the RMS of the whole projection (all heads together, ``eps`` inside the root) and
+    multiplied by these weights [nh d], [nkv d]; then rotary (rotate-half pairing) on the first ``rotary_dim``
+    dimensions of every head.  Returns q [n, nh d]; k goes to ``k_pool`` and the values — the keys as projected
+    (``values_from_keys``) or the columns behind k — to ``v_pool`` [pages, nkv, page_size, d] at ``slots``."""
+    _need(positions, "positions", torch.int32)
+    if proj.dtype not in DT_CODE or proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelError("qk_norm_rotary_store: proj must be a CUDA matrix with unit column stride")
+    n = proj.shape[0]
+    need_cols = (num_heads + (1 if values_from_keys else 2) * num_kv_heads) * head_dim
+    if proj.shape[1] < need_cols or positions.numel() != n:
+        raise KernelError("qk_norm_rotary_store: shapes do not agree")
+    normed = wq is not None
+    if normed:
+        _need(wq, "wq", torch.float32), _need(wk, "wk", torch.float32)
+        if wq.numel() != num_heads * head_dim or wk.numel() != num_kv_heads * head_dim:
+            raise KernelError("qk_norm_rotary_store: norm weights must cover the whole projections")
+    if rotary_dim:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("qk_norm_rotary_store: inv_freq must have rotary_dim / 2 entries")
+    if write_kv:
+        _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", proj.dtype), _need(v_pool, "v_pool", proj.dtype)
+        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pool.shape != v_pool.shape or slots.numel() != n:
+            raise KernelError("qk_norm_rotary_store: pool layout must be [pages, kv_heads, page_size, head_dim]")
+    q = torch.empty((n, num_heads * head_dim), dtype=proj.dtype, device=proj.device)
+    f = _fn("attention_prep.cu", "dli_qk_norm_rotary_store",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 10 + [c_void_p])
+    _check(f(_ptr(q), _ptr(proj), proj.stride(0), _ptr(wq), _ptr(wk), eps, _ptr(positions), _ptr(inv_freq if rotary_dim else None),
+             _ptr(slots if write_kv else None), _ptr(k_pool if write_kv else None), _ptr(v_pool if write_kv else None), n, num_heads,
+             num_kv_heads, head_dim, rotary_dim, page_size, int(write_kv), int(normed), int(values_from_keys), DT_CODE[proj.dtype], _stream()),
+           "qk_norm_rotary_store")
+    return q
+
+
+def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor) -> None:
+    """out *= sigmoid(gate), element by element; ``gate`` [n, cols] may be a column slice of a wider matrix."""
+    _need(out, "out")
+    n, cols = out.shape
+    if out.dtype not in DT_CODE or gate.dtype != out.dtype or tuple(gate.shape) != (n, cols) or gate.stride(1) != 1 or not gate.is_cuda:
+        raise KernelError("sigmoid_gate: shapes or dtype do not agree")
+    f = _fn("attention_prep.cu", "dli_sigmoid_gate", [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), c_void_p(gate.data_ptr()), gate.stride(0), n, cols, DT_CODE[out.dtype], _stream()), "sigmoid_gate")
+
+
+# ------------------------------------------------------------------ state-space mixer
+
+
+def _columns(u: torch.Tensor, name: str) -> None:
+    if u.dtype not in DT_CODE or u.dim() != 2 or not u.is_cuda or not u.is_contiguous():
+        raise KernelError(f"{name}: the projection must be a contiguous CUDA matrix")
+
+
+def causal_conv_silu(out: torch.Tensor, u: torch.Tensor, col0: int, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
+                     seq_of_token: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor) -> None:
+    """out[t, c] = silu(bias[c] + sum_j weight[c, j] * in(t - (taps - 1) + j, c)) for channels c = columns col0 .. of u.
+    The last tap weighs the token itself; in() before the step's first token of a sequence is the sequence's carried
+    input in ``state`` [slots, taps - 1, C] (oldest first).  ``conv_state_update`` moves the state on afterwards."""
+    _columns(u, "causal_conv_silu"), _need(out, "out", u.dtype), _need(weight, "weight", torch.float32), _need(state, "state", u.dtype)
+    _need(seq_of_token, "seq_of_token", torch.int32), _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
+    n, C = out.shape
+    taps = weight.shape[1]
+    if u.shape[0] != n or col0 + C > u.shape[1] or weight.shape[0] != C or tuple(state.shape[1:]) != (taps - 1, C) or seq_of_token.numel() != n:
+        raise KernelError("causal_conv_silu: shapes do not agree")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    f = _fn("ssm.cu", "dli_causal_conv_silu", [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(u), u.stride(0), col0, _ptr(weight), _ptr(bias), _ptr(state), _ptr(seq_of_token), _ptr(q_start), _ptr(state_slot),
+             n, C, taps, DT_CODE[u.dtype], _stream()), "causal_conv_silu")
+
+
+def conv_state_update(state: torch.Tensor, u: torch.Tensor, col0: int, q_start: torch.Tensor, state_slot: torch.Tensor) -> None:
+    """Each sequence's carried inputs ``state`` [slots, taps - 1, C] become the last taps - 1 inputs it has seen."""
+    _columns(u, "conv_state_update"), _need(state, "state", u.dtype), _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
+    _, keep, C = state.shape
+    if col0 + C > u.shape[1] or q_start.numel() != state_slot.numel() + 1:
+        raise KernelError("conv_state_update: shapes do not agree")
+    f = _fn("ssm.cu", "dli_conv_state_update", [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(state), _ptr(u), u.stride(0), col0, _ptr(q_start), _ptr(state_slot), state_slot.numel(), C, keep + 1, DT_CODE[u.dtype], _stream()),
+           "conv_state_update")
+
+
+SSM_SCAN_MAX_STATE = 256
+
+
+def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, groups: int) -> None:
+    """The selective scan of every sequence's tokens of this step, from and to its slot of ``state`` [slots, heads, N, P]
+    (float32).  xbc [n, heads P + 2 groups N] holds x | B | C; dt_raw is column dt_col + head of u.  Per head:
+    dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d_skip x.  y [n, heads P] float32."""
+    _columns(u, "ssm_scan"), _need(xbc, "xbc", u.dtype), _need(y, "y", torch.float32), _need(state, "state", torch.float32)
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        _need(t, name, torch.float32)
+    _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
+    _, heads, N, P = state.shape
+    n = xbc.shape[0]
+    if (xbc.shape[1] != heads * P + 2 * groups * N or tuple(y.shape) != (n, heads * P) or u.shape[0] != n or dt_col + heads > u.shape[1]
+            or heads % groups or N > SSM_SCAN_MAX_STATE or dt_bias.numel() != heads or a_log.numel() != heads or d_skip.numel() != heads
+            or q_start.numel() != state_slot.numel() + 1):
+        raise KernelError("ssm_scan: shapes do not agree (or the state size is above 256)")
+    f = _fn("ssm.cu", "dli_ssm_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+            + [c_int] * 6 + [c_void_p])
+    _check(f(_ptr(y), _ptr(xbc), _ptr(u), u.stride(0), dt_col, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(q_start),
+             _ptr(state_slot), state_slot.numel(), heads, P, N, groups, DT_CODE[u.dtype], _stream()), "ssm_scan")
+
+
+def gated_group_rmsnorm(out: torch.Tensor, y: torch.Tensor, u: torch.Tensor, z_col: int, weight: torch.Tensor, parts: int, eps: float) -> None:
+    """out = g / sqrt(mean(g^2) + eps) * weight with g = y * silu(z), the mean taken over each of ``parts`` equal runs
+    of the row; z is columns z_col .. of u; y float32."""
+    _columns(u, "gated_group_rmsnorm"), _need(out, "out", u.dtype), _need(y, "y", torch.float32), _need(weight, "weight", torch.float32)
+    n, inner = y.shape
+    if tuple(out.shape) != (n, inner) or u.shape[0] != n or z_col + inner > u.shape[1] or weight.numel() != inner or inner % parts:
+        raise KernelError("gated_group_rmsnorm: shapes do not agree")
+    f = _fn("ssm.cu", "dli_gated_group_rmsnorm", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(y), _ptr(u), u.stride(0), z_col, _ptr(weight), n, inner, parts, eps, DT_CODE[u.dtype], _stream()), "gated_group_rmsnorm")

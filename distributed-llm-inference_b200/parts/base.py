@@ -26,6 +26,9 @@ Interfaces by category (what a new part of that category must provide):
                   ``cache_need()`` says what its run step needs of the cache manager (usually its
                   mixer's answer; an arrangement with several mixers side by side returns all their
                   needs, and hands each mixer the same ``LayerCache``).
+``stream_entry``  ``apply(stream, batch)``: acts on the residual stream right before the layer of a run step that
+                  names it (``RunStep.entry``): what a looped span of layers adds to the stream at the start of
+                  a pass, for instance.  It settles the stream's pending delta first (``ResidualStream.settle``).
 ``embedding``     ``forward(token_ids) -> h`` float32 [n, H].
 ``head``          ``forward(y) -> logits`` float32 [k, V].
 
@@ -41,6 +44,10 @@ these is served with plain tensors:
   (it hands them to ``kernels.gemm.project`` or a decode product of ``kernels.ops``);
 * an arrangement with ``first_consumer() -> (norm, part)`` and ``defer_last_product(flag)`` lets
   the model extend this across layer borders.
+
+A sublayer's output that is normed before the residual addition stays pending as ``PendingNormed(a, norm)``:
+a norm with ``post_add_norm(h, a, post, rows=None) -> y`` (h += post(a); y = norm(h), one kernel) takes it as
+it is; any other reader gets it settled first (``post.add_into(h, a)``).
 """
 
 from __future__ import annotations
@@ -108,6 +115,16 @@ class PendingProduct:
         return project(self.x, self.weight)
 
 
+class PendingNormed:
+    """A sublayer's output ``a`` that is still to be normed by ``norm`` and then added to the residual stream:
+    the norm that reads the stream next may do all three steps in one kernel (``post_add_norm``)."""
+
+    __slots__ = ("a", "norm")
+
+    def __init__(self, a: torch.Tensor, norm) -> None:
+        self.a, self.norm = a, norm
+
+
 class ResidualStream:
     """The float32 residual h [n, H] and a delta (activation dtype) not yet added to it.
     Keeping the delta pending lets the next norm do the addition in the same kernel.  ``pending``
@@ -130,6 +147,15 @@ class ResidualStream:
     def take_pending(self):
         return self._pending
 
+    def settle(self) -> torch.Tensor:
+        """Add whatever is pending to h now and return h."""
+        delta, self._pending = self._pending, None
+        if isinstance(delta, PendingNormed):
+            delta.norm.add_into(self.h, delta.a)
+        elif delta is not None:
+            self.h += (delta.materialize() if isinstance(delta, PendingProduct) else delta).float()
+        return self.h
+
 
 def can_fuse(norm, consumer) -> bool:
     """Whether ``norm`` can compute a PendingProduct itself and ``consumer`` reads what it then returns."""
@@ -140,6 +166,14 @@ def normed_input(norm, h: torch.Tensor, delta, consumer, rows: torch.Tensor | No
     """norm(h + delta) as ``consumer`` will read it.  A delta that is still a PendingProduct goes,
     product and all, to a norm that can compute it (if the consumer reads ScaledRows and every row
     is wanted); otherwise it is computed first and the norm gets a tensor."""
+    if isinstance(delta, PendingNormed):
+        fused = getattr(norm, "post_add_norm", None)
+        if fused is not None:
+            return fused(h, delta.a, delta.norm, rows=rows)
+        if rows is not None:
+            raise TypeError("a normed delta that is still pending can only be read row by row by a norm with post_add_norm")
+        delta.norm.add_into(h, delta.a)
+        delta = None
     if isinstance(delta, PendingProduct):
         if rows is None and can_fuse(norm, consumer):
             y = norm.add_product_norm(h, delta)
@@ -151,7 +185,16 @@ def normed_input(norm, h: torch.Tensor, delta, consumer, rows: torch.Tensor | No
 
 _REGISTRY: dict[tuple[str, str], Callable[..., Any]] = {}
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "stream_entry")
+
+
+def tensor_name(spec: PartSpec, role: str, default: str) -> str:
+    """The checkpoint name of a part's tensor: ``spec.params["tensors"][role]`` (or ``spec.params["tensor"]`` for a
+    part with one tensor) where the architecture gives names of its own, else prefix + default."""
+    names = spec.params.get("tensors") or {}
+    if role in names:
+        return names[role]
+    return spec.params.get("tensor") or spec.prefix + default
 
 
 def register_part(category: str, kind: str):

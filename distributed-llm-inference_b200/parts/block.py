@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from .base import BuildEnv, Part, ResidualStream, build_part, can_fuse, normed_input, register_part
+from .base import BuildEnv, Part, PendingNormed, ResidualStream, build_part, can_fuse, normed_input, register_part
 
 
 @register_part("arrangement", "prenorm")
@@ -44,3 +44,43 @@ class PreNormBlock(Part):
         a = self.mixer.forward(y, batch, cache)
         y = normed_input(self.ffn_norm, stream.h, a, self.ffn)
         stream.pending = self.ffn.forward(y)
+
+
+@register_part("arrangement", "sandwich")
+class SandwichBlock(Part):
+    """x = x + post_a(mixer(pre_a(x))); x = x + post_f(ffn(pre_f(x))): every sublayer between two norms, the second
+    one on its output before the residual addition.  Roles: mixer_norm, mixer, mixer_post_norm, and — a layer
+    may have no feed-forward — ffn_norm, ffn, ffn_post_norm.  A sublayer's output stays pending with its norm
+    (``PendingNormed``), so the norm in front of the next sublayer norms it, adds it and norms the sum in one
+    kernel."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env: BuildEnv) -> None:
+        self.spec, self.env = spec, env
+        self.mixer_norm = build_part("norm", spec.parts["mixer_norm"], env)
+        self.mixer = build_part("mixer", spec.parts["mixer"], env)
+        self.mixer_post_norm = build_part("norm", spec.parts["mixer_post_norm"], env)
+        self.has_ffn = "ffn" in spec.parts
+        if self.has_ffn:
+            self.ffn_norm = build_part("norm", spec.parts["ffn_norm"], env)
+            self.ffn = build_part("feed_forward", spec.parts["ffn"], env)
+            self.ffn_post_norm = build_part("norm", spec.parts["ffn_post_norm"], env)
+        for norm in (self.mixer_post_norm, *([self.ffn_post_norm] if self.has_ffn else [])):
+            if not hasattr(norm, "add_into"):
+                raise ValueError("sandwich: the norm behind a sublayer must offer add_into(h, a)")
+
+    def children(self):
+        out = [self.mixer_norm, self.mixer, self.mixer_post_norm]
+        return out + ([self.ffn_norm, self.ffn, self.ffn_post_norm] if self.has_ffn else [])
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, stream: ResidualStream, batch, cache) -> None:
+        y = normed_input(self.mixer_norm, stream.h, stream.take_pending(), self.mixer)
+        pending = PendingNormed(self.mixer.forward(y, batch, cache), self.mixer_post_norm)
+        if self.has_ffn:
+            y = normed_input(self.ffn_norm, stream.h, pending, self.ffn)
+            pending = PendingNormed(self.ffn.forward(y), self.ffn_post_norm)
+        stream.pending = pending

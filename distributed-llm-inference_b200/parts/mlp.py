@@ -7,7 +7,7 @@ import torch
 from ..kernels import ops
 from ..kernels.gemm import dense_product, fused_epilogue, last_product, project
 from ..weights.loader import TensorDecl
-from .base import Part, register_part
+from .base import Part, register_part, tensor_name
 
 
 @register_part("feed_forward", "swiglu")
@@ -59,3 +59,32 @@ class SwiGLU(Part):
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
             ops.silu_mul(act, gate_up, self.tiled)
         return last_product(act, self.w_down, self.defer_output)
+
+
+@register_part("feed_forward", "dense_act")
+class DenseActMLP(Part):
+    """down(act(up(x))): a plain feed-forward without a gate.  params: hidden_size, intermediate_size, activation
+    (``relu2``: the square of relu; ``gelu_tanh``; ``silu``), tensors (names of up, down)."""
+
+    graph_capturable = True
+    takes_scaled_rows = False
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = spec.params.get("activation", "relu2")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not supported (known: {sorted(ops.ACTIVATIONS)})")
+        self.names = {"up": tensor_name(spec, "up", "up_proj.weight"), "down": tensor_name(spec, "down", "down_proj.weight")}
+        self.w_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+
+    def declare(self):
+        return {self.names["up"]: TensorDecl((self.inter, self.hidden)), self.names["down"]: TensorDecl((self.hidden, self.inter))}
+
+    def load(self, tensors):
+        self.w_up, self.w_down = tensors[self.names["up"]], tensors[self.names["down"]]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return project(ops.activation(project(x, self.w_up), self.activation), self.w_down)

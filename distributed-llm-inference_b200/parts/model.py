@@ -8,7 +8,7 @@ from ..config.spec import ModelSpec
 from ..kernels import ops
 from ..kernels.gemm import SKINNY_MAX_TOKENS_HEAD, linear, project
 from ..weights.loader import TensorDecl
-from .base import BuildEnv, Part, ResidualStream, build_part, can_fuse, normed_input, register_part
+from .base import BuildEnv, Part, ResidualStream, build_part, can_fuse, normed_input, register_part, tensor_name
 
 
 @register_part("embedding", "token_embedding")
@@ -20,13 +20,14 @@ class TokenEmbedding(Part):
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
+        self.name = tensor_name(spec, "weight", "weight")
         self.weight: torch.Tensor | None = None
 
     def declare(self):
-        return {self.spec.prefix + "weight": TensorDecl((self.vocab, self.hidden))}
+        return {self.name: TensorDecl((self.vocab, self.hidden))}
 
     def load(self, tensors):
-        self.weight = tensors[self.spec.prefix + "weight"]
+        self.weight = tensors[self.name]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         h = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
@@ -48,13 +49,14 @@ class LMHead(Part):
         super().__init__(spec, env)
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
         self.tied_to = spec.params.get("tied_to")
+        self.name = tensor_name(spec, "weight", "weight")
         self.weight: torch.Tensor | None = None
 
     def declare(self):
-        return {self.spec.prefix + "weight": TensorDecl((self.vocab, self.hidden), optional_alias_of=self.tied_to)}
+        return {self.name: TensorDecl((self.vocab, self.hidden), optional_alias_of=self.tied_to)}
 
     def load(self, tensors):
-        self.weight = tensors[self.tied_to or self.spec.prefix + "weight"]
+        self.weight = tensors[self.tied_to or self.name]
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
         return project(y, self.weight, out_dtype=torch.float32, max_tokens=SKINNY_MAX_TOKENS_HEAD)
@@ -77,8 +79,10 @@ class DecoderModel:
         self.env = BuildEnv(dtype, torch.device(device))
         self.embedding = build_part("embedding", spec.embedding, self.env)
         self.layers = [build_part("arrangement", layer, self.env) for layer in spec.layers]
+        self.entries = [build_part("stream_entry", entry, self.env) for entry in spec.entries]
         self.final_norm = build_part("norm", spec.final_norm, self.env)
         self.head = build_part("head", spec.head, self.env)
+        self.trace_layers: list | None = None  # set to a list to collect the stream after every layer run
         self._wire_deferred_products()
 
     def _wire_deferred_products(self) -> None:
@@ -108,7 +112,7 @@ class DecoderModel:
 
     def parts(self) -> list[Part]:
         out: list[Part] = []
-        for top in (self.embedding, *self.layers, self.final_norm, self.head):
+        for top in (self.embedding, *self.entries, *self.layers, self.final_norm, self.head):
             out.extend(_walk(top))
         return out
 
@@ -141,7 +145,11 @@ class DecoderModel:
         batch.scratch.clear()
         stream = ResidualStream(self.embedding.forward(batch.token_ids))
         for i, step in enumerate(self.spec.run_order):
+            if step.entry is not None:
+                self.entries[step.entry].apply(stream, batch)
             self.layers[step.layer].forward(stream, batch, caches[i])
+            if self.trace_layers is not None:  # a debugging aid: the stream after every layer run
+                self.trace_layers.append(ResidualStream(stream.h.clone(), stream.take_pending()).settle())
         if batch.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         rows = None if getattr(batch, "logits_all_rows", False) else batch.logit_rows

@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import Part, register_part
+from .base import Part, register_part, tensor_name
 
 
 @register_part("norm", "rmsnorm")
@@ -42,3 +42,49 @@ class RMSNorm(Part):
         if not ops.skinny_gemm_supported(h.shape[0], self.size) or h.shape[0] > 64:
             return None  # the product that reads the result could not take rows of this size
         return ops.skinny_gemm_residual(product.x, product.weight, h, self.weight, self.eps)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """y = (v - mean(v)) / sqrt(var(v) + eps) * weight, var the mean of the squared deviations, no bias; float32
+    arithmetic, one rounding.  params: size, eps, tensor (the weight's name; default prefix + "weight").
+
+    Besides ``add_norm`` (v = h + delta) it norms on both sides of the residual addition in one kernel:
+    ``post_add_norm(h, a, post)`` is h += post(a), y = self(h), for layers whose sublayer outputs are normed
+    before they are added; ``add_into(h, a)`` is the first half alone."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.name = tensor_name(spec, "weight", "weight")
+        self.weight: torch.Tensor | None = None
+
+    def declare(self):
+        return {self.name: TensorDecl((self.size,), "vector32")}
+
+    def load(self, tensors):
+        self.weight = tensors[self.name]
+
+    def _out(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
+        n = h.shape[0] if rows is None else rows.numel()
+        return torch.empty((n, self.size), dtype=self.env.dtype, device=h.device)
+
+    def add_norm(self, h: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None) -> torch.Tensor:
+        if delta is not None:
+            if rows is not None:
+                raise ValueError("layernorm: a plain delta is added to the whole stream (rows=None)")
+            h += delta.float()
+        y = self._out(h, rows)
+        ops.post_add_layernorm(y, h, None, None, self.weight, 0.0, self.eps, rows)
+        return y
+
+    def post_add_norm(self, h: torch.Tensor, a: torch.Tensor, post: "LayerNorm", rows: torch.Tensor | None = None) -> torch.Tensor:
+        y = self._out(h, rows)
+        ops.post_add_layernorm(y, h, a, post.weight, self.weight, post.eps, self.eps, rows)
+        return y
+
+    def add_into(self, h: torch.Tensor, a: torch.Tensor) -> None:
+        ops.post_add_layernorm(None, h, a, self.weight, None, self.eps, 0.0)

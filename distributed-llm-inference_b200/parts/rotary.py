@@ -74,6 +74,13 @@ def _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv
     return _rotate_and_store(project(x, wqkv), batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq, table_key)
 
 
+def _norm_rotate_and_store(proj, wq, wk, eps, batch, cache, num_heads, num_kv_heads, write_kv, values_from_keys, head_dim, rotary_dim, inv_freq):
+    group = batch.group(cache.group)
+    return ops.qk_norm_rotary_store(proj, wq, wk, eps, batch.positions, inv_freq, group.slots if write_kv else None,
+                                    cache.k if write_kv else None, cache.v if write_kv else None, num_heads, num_kv_heads, head_dim,
+                                    rotary_dim, cache.page_size, write_kv, values_from_keys)
+
+
 @register_part("position", "rotary")
 class Rotary(Part):
     """params: head_dim, rotary_dim (<= head_dim; elements beyond it pass through), theta,
@@ -99,6 +106,13 @@ class Rotary(Part):
     def project_and_encode(self, x, wqkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
         return _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq, self.table_key)
 
+    def norm_rotate_and_store(self, proj, wq, wk, eps: float, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool,
+                              values_from_keys: bool):
+        """For a mixer that norms q and k over their whole projection before the encoding: norm (if ``wq``), rotation
+        and cache write in one kernel; returns the encoded queries [n, num_heads * head_dim]."""
+        return _norm_rotate_and_store(proj, wq, wk, eps, batch, cache, num_heads, num_kv_heads, write_kv, values_from_keys,
+                                      self.head_dim, self.rotary_dim, self.inv_freq)
+
 
 @register_part("position", "none")
 class NoPosition(Part):
@@ -115,3 +129,8 @@ class NoPosition(Part):
 
     def project_and_encode(self, x, wqkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
         return _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, 0, None)
+
+    def norm_rotate_and_store(self, proj, wq, wk, eps: float, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool,
+                              values_from_keys: bool):
+        return _norm_rotate_and_store(proj, wq, wk, eps, batch, cache, num_heads, num_kv_heads, write_kv, values_from_keys,
+                                      self.head_dim, 0, None)

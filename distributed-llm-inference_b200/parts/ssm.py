@@ -1,0 +1,86 @@
+"""State-space mixers: per-request state of fixed size instead of keys and values in pages."""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.needs import StateNeed
+from ..kernels import ops
+from ..kernels.gemm import project
+from ..weights.loader import TensorDecl
+from .base import Part, register_part, tensor_name
+
+
+@register_part("mixer", "mamba2")
+class Mamba2Mixer(Part):
+    """Mamba-2 (state-space duality) on any mix of prompt portions and decoded tokens.
+
+    The input projection yields z | x | B | C | dt (inner = num_heads * head_dim columns each for z and x,
+    groups * state_size each for B and C, one dt per head).  x | B | C pass a causal convolution per channel
+    (``conv_taps`` taps, bias) and SiLU.  Per head, with dt = softplus(dt + dt_bias) and its group's B and C:
+
+        S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T        (S: state_size x head_dim, float32)
+        y_t = S_t^T C_t + D x_t
+
+    y * silu(z) is divided by its RMS in ``norm_groups`` equal parts of the row, multiplied by a weight, and goes
+    through the output projection.  A request keeps S and the convolution's last taps - 1 inputs in its state
+    slot; both start at zero.  The step sizes, decays, the state and every sum of the recurrence are float32.
+
+    params: hidden_size, num_heads, head_dim, state_size, groups, conv_taps, norm_groups, eps, tensors (names of
+    in, conv, conv_bias, dt_bias, A_log, D, norm, o)."""
+
+    graph_capturable = False  # padding rows of a replayed graph would touch a state slot
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.P, self.N = int(p["num_heads"]), int(p["head_dim"]), int(p["state_size"])
+        self.groups, self.taps, self.parts = int(p["groups"]), int(p["conv_taps"]), int(p["norm_groups"])
+        self.eps = float(p["eps"])
+        if self.heads % self.groups or (self.heads * self.P) % self.parts or self.taps < 1:
+            raise ValueError("mamba2: heads must be a multiple of groups, heads * head_dim of norm_groups, and conv_taps >= 1")
+        if self.N > ops.SSM_SCAN_MAX_STATE:
+            raise ValueError(f"mamba2: state_size={self.N} is above the scan kernel's {ops.SSM_SCAN_MAX_STATE}")
+        self.inner = self.heads * self.P
+        self.channels = self.inner + 2 * self.groups * self.N
+        self.names = {role: tensor_name(spec, role, default) for role, default in (
+            ("in", "in_proj.weight"), ("conv", "conv1d.weight"), ("conv_bias", "conv1d.bias"), ("dt_bias", "dt_bias"),
+            ("A_log", "A_log"), ("D", "D"), ("norm", "norm.weight"), ("o", "out_proj.weight"))}
+        self.w: dict[str, torch.Tensor] = {}
+
+    def declare(self):
+        nm = self.names
+        return {
+            nm["in"]: TensorDecl((self.inner + self.channels + self.heads, self.hidden)),
+            nm["conv"]: TensorDecl((self.channels, self.taps), "vector32"),
+            nm["conv_bias"]: TensorDecl((self.channels,), "vector32"),
+            nm["dt_bias"]: TensorDecl((self.heads,), "vector32"),
+            nm["A_log"]: TensorDecl((self.heads,), "vector32"),
+            nm["D"]: TensorDecl((self.heads,), "vector32"),
+            nm["norm"]: TensorDecl((self.inner,), "vector32"),
+            nm["o"]: TensorDecl((self.hidden, self.inner)),
+        }
+
+    def load(self, tensors):
+        self.w = {role: tensors[name] for role, name in self.names.items()}
+
+    def cache_need(self):
+        """The recurrent state (float32) and the convolution's carried inputs (activation dtype), per request."""
+        return (StateNeed((self.heads, self.N, self.P), torch.float32), StateNeed((self.taps - 1, self.channels), self.env.dtype))
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        w = self.w
+        n = x.shape[0]
+        ssm_state, conv_state = cache.states
+        u = project(x, w["in"])  # z | x | B | C | dt
+        xbc = torch.empty((n, self.channels), dtype=x.dtype, device=x.device)
+        ops.causal_conv_silu(xbc, u, self.inner, w["conv"], w["conv_bias"], conv_state, batch.seq_of_token, batch.q_start, batch.state_slot)
+        if self.taps > 1:
+            ops.conv_state_update(conv_state, u, self.inner, batch.q_start, batch.state_slot)
+        y = torch.empty((n, self.inner), dtype=torch.float32, device=x.device)
+        ops.ssm_scan(y, xbc, u, self.inner + self.channels, w["dt_bias"], w["A_log"], w["D"], ssm_state, batch.q_start, batch.state_slot,
+                     self.groups)
+        gated = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
+        ops.gated_group_rmsnorm(gated, y, u, 0, w["norm"], self.parts, self.eps)
+        return project(gated, w["o"])

@@ -11,8 +11,8 @@ function, cache manager and kernels (nothing is sampled).  For a step in which
 logits are wanted, ``DIR/<step>.f32`` holds them as little-endian float32
 [wanted, vocab], in the order of the entries and of ``want``.  After every
 step a line ``done <step>`` is printed.  The cache pool holds ``--max-tokens``
-tokens (in pages of ``--page-size``), so pages of finished requests are used
-again.
+tokens (in pages of ``--page-size``) and has ``--max-requests`` state slots, so
+pages and slots of finished requests are used again.
 
 With ``--prefix-caching`` the cache manager's prefix index is on: full pages of a finished (or live)
 request stay findable by the hash chain of their tokens, and a new request whose tokens begin the
@@ -36,6 +36,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--out", required=True, help="folder the logits files are written to")
     ap.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests that are live at any time (default 4)")
     ap.add_argument("--prefix-caching", action="store_true", help="reuse indexed pages of earlier requests that begin with the same tokens")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
@@ -49,7 +50,7 @@ def main(argv: list[str] | None = None) -> int:
     out_dir.mkdir(parents=True, exist_ok=True)
     model = load_model(args.model, args.dtype, args.device)
     pages = max(1, -(-args.max_tokens // args.page_size))
-    runner = ModelRunner(model, num_pages=pages, page_size=args.page_size, max_requests=8,
+    runner = ModelRunner(model, num_pages=pages, page_size=args.page_size, max_requests=args.max_requests,
                          enable_prefix_caching=args.prefix_caching, watermark=0.0)
     manager = runner.manager
     print(f"[trace_run] ready: {pages} pages of {args.page_size} tokens", file=sys.stderr, flush=True)

@@ -78,7 +78,7 @@ def silu_mul(out, gate_up, tiled=False):
     out.copy_((g / (1 + torch.exp(-g)) * up.float()).to(out.dtype))
 
 
-def paged_attention_simt(out, qkv, k_pool, v_pool, block_tables, seq_of_token, positions, num_heads, scale, window=None):
+def paged_attention_simt(out, qkv, k_pool, v_pool, block_tables, seq_of_token, positions, num_heads, scale, window=None, sink=None):
     n = out.shape[0]
     _, nkv, page_size, d = k_pool.shape
     fan = num_heads // nkv
@@ -94,11 +94,13 @@ def paged_attention_simt(out, qkv, k_pool, v_pool, block_tables, seq_of_token, p
         v = v_pool[pages, :, (keys % page_size).long(), :].float()
         k, v = k.repeat_interleave(fan, 1), v.repeat_interleave(fan, 1)  # [keys, nh, d]
         s = torch.einsum("hd,khd->hk", q[t], k) * scale
-        w = torch.softmax(s, -1)
+        if sink is not None:  # one more term in the denominator, without a value
+            s = torch.cat([s, torch.full((num_heads, 1), float(sink))], -1)
+        w = torch.softmax(s, -1)[:, : keys.numel()]
         out[t] = torch.einsum("hk,khd->hd", w, v).reshape(-1).to(out.dtype)
 
 
-def _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window):
+def _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window, sink=None):
     """The bfloat16 attention kernels' common contract: sequences [seq0, seq0 + num_seqs); a sequence's
     tokens sit in rows q_start[s] .. q_start[s + 1] at positions kv_len[s] - q_len .. kv_len[s] - 1."""
     rows, seqs, pos = [], [], []
@@ -112,25 +114,145 @@ def _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_s
     idx = torch.tensor(rows)
     part = torch.empty((len(rows), out.shape[1]), dtype=out.dtype)
     paged_attention_simt(part, qkv[idx], k_pool, v_pool, block_tables, torch.tensor(seqs, dtype=torch.int32),
-                         torch.tensor(pos, dtype=torch.int32), num_heads, scale, window)
+                         torch.tensor(pos, dtype=torch.int32), num_heads, scale, window, sink)
     out[idx] = part
 
 
 def paged_attention_mma(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, max_q_len, first_row, num_heads, scale,
-                        window=None, splits=1, scratch=None):
+                        window=None, splits=1, scratch=None, sink=None):
     assert splits == 1 or (max_q_len == 1 and scratch is not None)
-    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window)
+    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window, sink)
 
 
 def paged_decode_tma(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, first_row, num_heads, scale,
-                     window=None, splits=1, scratch=None, max_kv_len=0):
+                     window=None, splits=1, scratch=None, max_kv_len=0, sink=None):
     assert splits == 1 or scratch is not None
-    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window)
+    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window, sink)
 
 
 def paged_prefill_tc(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, max_q_len, num_heads, scale,
-                     window=None, query_tiles=0):
-    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window)
+                     window=None, query_tiles=0, sink=None):
+    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window, sink)
+
+
+# ---- layer norm around the residual stream, activations
+
+
+def _ln(x, eps):
+    mu = x.mean(-1, keepdim=True)
+    return (x - mu) / torch.sqrt(((x - mu) ** 2).mean(-1, keepdim=True) + eps)
+
+
+def post_add_layernorm(y, h, a, w_post, w_pre, eps_post, eps_pre, rows=None):
+    idx = slice(None) if rows is None else rows.long()
+    v = h[idx]
+    if a is not None:
+        v = v + _ln(a[idx].float(), eps_post) * w_post
+        if rows is None:
+            h.copy_(v)
+    if y is not None:
+        y.copy_((_ln(v, eps_pre) * w_pre).to(y.dtype))
+
+
+def stream_reinject(h, table, ids, vec):
+    if table is not None:
+        h += table[ids.long()].float()
+    if vec is not None:
+        h += vec
+
+
+def activation(x, kind):
+    z = x.float()
+    if kind == "relu2":
+        z = torch.relu(z) ** 2
+    elif kind == "gelu_tanh":
+        z = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z**3)))
+    else:
+        z = z / (1 + torch.exp(-z))
+    x.copy_(z.to(x.dtype))
+    return x
+
+
+# ---- between an attention mixer's projections and its kernel
+
+
+def qk_norm_rotary_store(proj, wq, wk, eps, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim, rotary_dim,
+                         page_size, write_kv=True, values_from_keys=True):
+    n = proj.shape[0]
+    nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+    q, k = proj[:, :nq].float(), proj[:, nq : nq + nk].float()
+    v = proj[:, nq : nq + nk] if values_from_keys else proj[:, nq + nk : nq + 2 * nk]
+    if wq is not None:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * wq
+        k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * wk
+    qk = torch.cat([q, k], -1).view(n, num_heads + num_kv_heads, head_dim).clone()
+    if rotary_dim:
+        half = rotary_dim // 2
+        ang = positions.float()[:, None] * inv_freq[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        lo, hi = qk[..., :half].clone(), qk[..., half:rotary_dim].clone()
+        qk[..., :half] = lo * cos - hi * sin
+        qk[..., half:rotary_dim] = hi * cos + lo * sin
+    if write_kv:
+        page, off = (slots // page_size).long(), (slots % page_size).long()
+        k_pool[page, :, off, :] = qk[:, num_heads:].to(k_pool.dtype)
+        v_pool[page, :, off, :] = v.reshape(n, num_kv_heads, head_dim).to(v_pool.dtype)
+    return qk[:, :num_heads].reshape(n, nq).to(proj.dtype)
+
+
+def sigmoid_gate(out, gate):
+    out.copy_((out.float() * torch.sigmoid(gate.float())).to(out.dtype))
+
+
+# ---- state-space mixer
+
+
+def _silu(x):
+    return x / (1 + torch.exp(-x))
+
+
+def causal_conv_silu(out, u, col0, weight, bias, state, seq_of_token, q_start, state_slot):
+    n, C = out.shape
+    taps = weight.shape[1]
+    for t in range(n):
+        s = int(seq_of_token[t])
+        first, slot = int(q_start[s]), int(state_slot[s])
+        acc = bias.clone() if bias is not None else torch.zeros(C)
+        for j in range(taps):
+            r = t - first - (taps - 1) + j
+            x = u[first + r, col0 : col0 + C] if r >= 0 else state[slot, taps - 1 + r]
+            acc = acc + weight[:, j] * x.float()
+        out[t] = _silu(acc).to(out.dtype)
+
+
+def conv_state_update(state, u, col0, q_start, state_slot):
+    _, keep, C = state.shape
+    for s in range(state_slot.numel()):
+        first, last, slot = int(q_start[s]), int(q_start[s + 1]), int(state_slot[s])
+        seen = torch.cat([state[slot], u[first:last, col0 : col0 + C]], 0)
+        state[slot] = seen[seen.shape[0] - keep :]
+
+
+def ssm_scan(y, xbc, u, dt_col, dt_bias, a_log, d_skip, state, q_start, state_slot, groups):
+    _, heads, N, P = state.shape
+    inner = heads * P
+    for s in range(state_slot.numel()):
+        slot = int(state_slot[s])
+        for t in range(int(q_start[s]), int(q_start[s + 1])):
+            x = xbc[t, :inner].float().view(heads, P)
+            B = xbc[t, inner : inner + groups * N].float().view(groups, N).repeat_interleave(heads // groups, 0)
+            C = xbc[t, inner + groups * N :].float().view(groups, N).repeat_interleave(heads // groups, 0)
+            dt = torch.nn.functional.softplus(u[t, dt_col : dt_col + heads].float() + dt_bias, threshold=20.0)
+            decay = torch.exp(-torch.exp(a_log) * dt)
+            state[slot] = decay[:, None, None] * state[slot] + (dt[:, None] * B)[:, :, None] * x[:, None, :]
+            y[t] = (torch.einsum("hnp,hn->hp", state[slot], C) + d_skip[:, None] * x).reshape(-1)
+
+
+def gated_group_rmsnorm(out, y, u, z_col, weight, parts, eps):
+    n, inner = y.shape
+    g = (y * _silu(u[:, z_col : z_col + inner].float())).view(n, parts, inner // parts)
+    g = g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)
+    out.copy_((g.view(n, inner) * weight).to(out.dtype))
 
 
 # ---- the decode matrix product and its epilogues (bfloat16 in, float32 sums)
@@ -261,7 +383,9 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "skinny_gemm_slices": skinny_gemm_slices, "skinny_gemm": skinny_gemm, "skinny_gemm_residual": skinny_gemm_residual,
        "skinny_gemm_swiglu": skinny_gemm_swiglu, "skinny_gemm_rotary": skinny_gemm_rotary, "dense_gemm": dense_gemm,
        "dense_gemm_swiglu": dense_gemm_swiglu, "dense_gemm_rotary": dense_gemm_rotary,
-       "sample": sample}
+       "sample": sample, "post_add_layernorm": post_add_layernorm, "stream_reinject": stream_reinject, "activation": activation,
+       "qk_norm_rotary_store": qk_norm_rotary_store, "sigmoid_gate": sigmoid_gate, "causal_conv_silu": causal_conv_silu,
+       "conv_state_update": conv_state_update, "ssm_scan": ssm_scan, "gated_group_rmsnorm": gated_group_rmsnorm}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered
