@@ -76,17 +76,17 @@ def sink_softmax(scores):
     return e / (math.exp(-m) + e.sum())
 
 
-def sink_attention(h, w, px, mix, eps, positions=None):
+def sink_attention(h, w, px, mix, eps):
     """The attention mixer on a whole sequence h [T, width].
 
     q = Wq h, k = Wk h; the values are k as projected (no norm, no rotation, no value matrix);
     q and k are each divided by the RMS of their whole projection (all heads together) and
     multiplied by a weight of that size; rotary on the first ``rot.dims`` dimensions of each
-    head; scores (q . k) * scale over keys j <= i with the sink softmax; the heads' outputs
-    times sigmoid(Wg h), then Wo."""
+    head; scores (q . k) * scale over keys j <= i (the last ``window`` of them, if the mixer
+    has that key) with the sink softmax; the heads' outputs times sigmoid(Wg h), then Wo."""
     T = h.shape[0]
     H, G, d, dv = mix["heads"], mix["kv_heads"], mix["dim"], mix["vdim"]
-    pos = np.arange(T, dtype=np.float64) if positions is None else positions
+    pos = np.arange(T, dtype=np.float64)
     q = h @ w[px + "q"].T
     k = h @ w[px + "k"].T
     v = k.reshape(T, G, d)
@@ -98,11 +98,12 @@ def sink_attention(h, w, px, mix, eps, positions=None):
     kn = rotate_half_pairs(kn, pos, rot["dims"], rot["base"], factor)
     out = np.zeros((T, H, dv), dtype=h.dtype)
     for i in range(T):
+        lo = max(0, i - mix["window"] + 1) if mix.get("window") else 0
         for a in range(H):
             g = a // (H // G)
-            s = (kn[: i + 1, g] @ q[i, a]) * mix["scale"]
+            s = (kn[lo : i + 1, g] @ q[i, a]) * mix["scale"]
             p = sink_softmax(s)
-            out[i, a] = p @ v[: i + 1, g]
+            out[i, a] = p @ v[lo : i + 1, g]
     gate = sigmoid(h @ w[px + "g"].T)
     return (out.reshape(T, H * dv) * gate) @ w[px + "o"].T
 
