@@ -388,6 +388,180 @@ def more_points(model_1b, steps, warmup, pk):
     return out
 
 
+# ----------------------------------------------------------------------------- --design: another architecture beside Llama
+
+
+def pazenex_sizes(width, heads, kv_heads, dim, ssm_heads, state, groups, ff, vocab=32000):
+    """A Pazenex model of eight layer runs (attention, Mamba-2, attention, Mamba-2, the four run twice) and the Llama
+    configuration of the same width, heads, feed-forward size and number of layers."""
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim**-0.5,
+                     "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0}}}}
+    ssm = {"type": "mamba2", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": ssm_heads, "vdim": 64, "state": state, "groups": groups, "conv": 4, "norm_groups": groups}}
+    pz = {"architecture": "Pazenex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": [att, ssm, att, ssm],
+          "loop": {"start": 0, "stop": 4, "times": 2}}
+    llama = dict(LLAMA_3_2_1B, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=dim,
+                 intermediate_size=ff, num_hidden_layers=8, vocab_size=vocab, tie_word_embeddings=False)
+    return pz, llama
+
+
+DESIGN_SIZES = {
+    "w1024": dict(width=1024, heads=16, kv_heads=4, dim=64, ssm_heads=32, state=64, groups=4, ff=4096),
+    "w2048": dict(width=2048, heads=32, kv_heads=8, dim=64, ssm_heads=64, state=128, groups=8, ff=8192),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ssm_heads=128, state=128, groups=8, ff=14336),
+}
+
+
+def all_weight_bytes(model):
+    seen, total = set(), 0
+
+    def walk(v):
+        nonlocal total
+        if hasattr(v, "data_ptr") and hasattr(v, "numel"):
+            if v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                total += v.numel() * v.element_size()
+        elif isinstance(v, dict):
+            for x in v.values():
+                walk(x)
+
+    for part in model.parts():
+        for v in vars(part).values():
+            walk(v)
+    return total
+
+
+def time_kernel(fn, reps=7, warmup=3):
+    """Median device time of fn() in microseconds; a 256 MB buffer is written between calls, so nothing stays in L2."""
+    import torch
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for i in range(warmup + reps):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(end) * 1e3)
+    return statistics.median(times)
+
+
+def design_kernels(size, pk, tokens=4096, seqs=64):
+    """Every kernel of the new parts beside the like kernel of the Llama parts, at one size: a prompt portion of ``tokens``
+    tokens and a decode step of ``seqs`` sequences.  us, the bytes (or operations) the kernel has to move, and the share
+    of the measured HBM peak (of the CUDA cores' float32 rate for the scan over a portion)."""
+    import torch
+
+    from dli_b200.kernels import ops
+
+    dev, bf = "cuda", torch.bfloat16
+    W, nh, nkv, d = size["width"], size["heads"], size["kv_heads"], size["dim"]
+    Hs, P, N, G, taps, ff = size["ssm_heads"], 64, size["state"], size["groups"], 4, size["ff"]
+    inner = Hs * P
+    C = inner + 2 * G * N
+    out = {}
+
+    def record(name, us, nbytes, like=None, flops=None):
+        rec = {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops is not None:
+            rec["tflops_fp32"] = round(flops / us / 1e6, 2)
+            rec["simt_frac"] = round(flops / us / 1e6 / SIMT_FP32_TFLOPS, 3)
+        if like:
+            rec["like"] = like
+        out[name] = rec
+
+    for label, n, S in (("portion", tokens, 1), ("decode", seqs, seqs)):
+        q_lens = [n // S] * S
+        q_start = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        seq_of = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), n // S).to(dev)
+        slot = torch.arange(S, dtype=torch.int32, device=dev)
+        positions = torch.arange(n, dtype=torch.int32, device=dev) % (n // S) + (0 if S == 1 else 2047)
+        h = torch.randn(n, W, device=dev)
+        a = torch.randn(n, W, device=dev).to(bf)
+        w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+        y = torch.empty(n, W, dtype=bf, device=dev)
+        record(f"{label}.post_add_layernorm", time_kernel(lambda: ops.post_add_layernorm(y, h, a, w1, w2, 1e-6, 1e-6)), n * W * 12, "add_rmsnorm")
+        record(f"{label}.add_rmsnorm", time_kernel(lambda: ops.add_rmsnorm(y, h, a, w1, 1e-6)), n * W * 12)
+        # attention preparation
+        page, pages = 16, (n if S == 1 else S) // 16 + 2
+        slots = torch.arange(n, dtype=torch.int32, device=dev)
+        kp, vp = (torch.zeros(pages + n // 16, nkv, page, d, dtype=bf, device=dev) for _ in range(2))
+        inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2).float() / d))).to(dev)
+        proj = torch.randn(n, (2 * nh + nkv) * d, device=dev).to(bf)
+        wq, wk = torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev)
+        moved = n * ((nh + nkv) * d * 2 + (nh + 2 * nkv) * d * 2)
+        record(f"{label}.qk_norm_rotary_store", time_kernel(lambda: ops.qk_norm_rotary_store(proj, wq, wk, 1e-6, positions, inv, slots, kp, vp, nh, nkv, d, d, page)),
+               moved, "rotary_store")
+        qkv = torch.randn(n, (nh + 2 * nkv) * d, device=dev).to(bf)
+        record(f"{label}.rotary_store", time_kernel(lambda: ops.rotary_store(qkv, positions, inv, slots, kp, vp, nh, nkv, d, d, page)),
+               n * ((nh + nkv) * d * 4 + nkv * d * 4))
+        att = torch.randn(n, nh * d, device=dev).to(bf)
+        gate = proj[:, (nh + nkv) * d :]
+        record(f"{label}.sigmoid_gate", time_kernel(lambda: ops.sigmoid_gate(att, gate)), n * nh * d * 6, "silu_mul")
+        up = torch.randn(n, ff, device=dev).to(bf)
+        record(f"{label}.activation_relu2", time_kernel(lambda: ops.activation(up, "relu2")), n * ff * 4, "silu_mul")
+        gu = torch.randn(n, 2 * ff, device=dev).to(bf)
+        act = torch.empty(n, ff, dtype=bf, device=dev)
+        record(f"{label}.silu_mul", time_kernel(lambda: ops.silu_mul(act, gu)), n * ff * 6)
+        # state-space mixer
+        u = torch.randn(n, inner + C + Hs, device=dev).to(bf)
+        xbc = torch.empty(n, C, dtype=bf, device=dev)
+        cw, cb = torch.randn(C, taps, device=dev), torch.randn(C, device=dev)
+        cstate = torch.zeros(S, taps - 1, C, dtype=bf, device=dev)
+        record(f"{label}.causal_conv_silu", time_kernel(lambda: ops.causal_conv_silu(xbc, u, inner, cw, cb, cstate, seq_of, q_start, slot)),
+               n * C * 4 + (S * (taps - 1) * C * 2 if S > 1 else 0), "silu_mul")
+        state = torch.zeros(S, Hs, N, P, device=dev)
+        ys = torch.empty(n, inner, device=dev)
+        dtb, al, dk = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
+        scan_us = time_kernel(lambda: ops.ssm_scan(ys, xbc, u, inner + C, dtb, al, dk, state, q_start, slot, G))
+        scan_bytes = S * Hs * N * P * 8 + n * (C * 2 + inner * 4)
+        record(f"{label}.ssm_scan", scan_us, scan_bytes, "decode attention" if S > 1 else "prefill attention", flops=5.0 * n * Hs * N * P)
+        gated = torch.empty(n, inner, dtype=bf, device=dev)
+        nw = torch.ones(inner, device=dev)
+        record(f"{label}.gated_group_rmsnorm", time_kernel(lambda: ops.gated_group_rmsnorm(gated, ys, u, 0, nw, G, 1e-6)), n * inner * 8, "add_rmsnorm")
+    return out
+
+
+SIMT_FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12  # CUDA-core multiply-adds of a B200 at 1.9 GHz: the scan's ceiling (no float32 tensor-core path)
+
+
+def design_arm(args) -> int:
+    """``--design pazenex``: prefill and decode throughput of Pazenex models with random weights at layer sizes that resemble
+    real models, beside Llama models of the same width, heads, feed-forward size and number of layer runs; and every
+    kernel of the new parts beside its like among the Llama parts."""
+    import torch
+
+    import dli_b200
+
+    pk = peaks()
+    line = {"design": args.design, "dtype": "bf16", "data": "synthetic: uniform-random token ids, seeded random weights", "sizes": {},
+            "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "simt_fp32_tflops": round(SIMT_FP32_TFLOPS, 1), "source": pk["source"]}}
+    names = [args.size] if args.size else list(DESIGN_SIZES)
+    for name in names:
+        pz_cfg, llama_cfg = pazenex_sizes(**DESIGN_SIZES[name])
+        rec = {}
+        for label, cfg in (("pazenex", pz_cfg), ("llama", llama_cfg)):
+            model = dli_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            wbytes = all_weight_bytes(model)
+            prefill = prefill_timed(model, llama_cfg, 8, pk["bf16_tflops"], reps=3, warmup=3, tokens=args.prompt_len)
+            decode = decode_device_timed(model, args.batch, args.steps, args.warmup, blocks=1, prompt_len=args.prompt_len,
+                                         context=args.prompt_len + 512)
+            rec[label] = {"prefill_tok_s": round(prefill["value"], 1), "prefill_ms": round(prefill["ms"], 3),
+                          "decode_tok_s": round(decode["tok_s"], 1), "decode_ms": round(decode["ms"], 4), "decode_launches": decode["launches"],
+                          "weight_bytes": wbytes, "decode_weight_gb_s": round(wbytes / decode["ms"] / 1e6, 1)}
+            del model
+            torch.cuda.empty_cache()
+        line["sizes"][name] = rec
+    if not args.skip_points:
+        line["kernels"] = design_kernels(DESIGN_SIZES[args.size or "w2048"], pk)
+    print(json.dumps(line))
+    return 0
+
+
 def config_record(cfg, layers, batch, source, extra=None):
     rec = {
         "model": "Llama-3.2-1B shape", "layers": layers, "layers_full": LLAMA_3_2_1B["num_hidden_layers"],
@@ -588,6 +762,9 @@ def main() -> int:
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "sample"],
                     help="profiling runs: only the device-timed decode steps, only the prefill step, or only the sampling kernel (prints a short line)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the step's kernels one by one")
+    ap.add_argument("--design", default=None, choices=["pazenex"],
+                    help="another measurement: this architecture beside Llama at equal sizes, and its kernels beside their likes (prints its own line)")
+    ap.add_argument("--size", default=None, choices=list(DESIGN_SIZES), help="--design: one size only")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="profiling runs: the context at which decoding starts (--phase decode), the prompt's length (--phase prefill)")
     args = ap.parse_args()
@@ -598,6 +775,8 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_arm(args)
 
     import torch
 
