@@ -514,7 +514,7 @@ def design_kernels(size, pk, tokens=4096, seqs=64):
         cstate = torch.zeros(S, taps - 1, C, dtype=bf, device=dev)
         record(f"{label}.causal_conv_silu", time_kernel(lambda: ops.causal_conv_silu(xbc, u, inner, cw, cb, cstate, seq_of, q_start, slot)),
                n * C * 4 + (S * (taps - 1) * C * 2 if S > 1 else 0), "silu_mul")
-        state = torch.zeros(S, Hs, N, P, device=dev)
+        state = torch.zeros(S, Hs, P, N, device=dev)
         ys = torch.empty(n, inner, device=dev)
         dtb, al, dk = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
         scan_us = time_kernel(lambda: ops.ssm_scan(ys, xbc, u, inner + C, dtb, al, dk, state, q_start, slot, G))

@@ -70,6 +70,7 @@ class CachePools:
             shape = (len(own), pages + 1, need.num_kv_heads, page_size, need.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
             self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+        self.scratch_state_slot = max_requests
         self.layer_caches: list[LayerCache] = []
         for i, answer in enumerate(needs):
             src = run_order[i].cache_of
@@ -77,7 +78,8 @@ class CachePools:
                 base = self.layer_caches[src]
                 self.layer_caches.append(LayerCache(base.group, base.k, base.v, page_size, writes=False, states=base.states))
                 continue
-            states = tuple(torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device) for need in state_needs_of(answer))
+            # one slot more than the manager hands out: padding rows of a replayed graph keep their state there
+            states = tuple(torch.zeros((max_requests + 1, *need.shape), dtype=need.dtype, device=device) for need in state_needs_of(answer))
             if paged_need_of(answer) is not None:  # pages, and state slots beside them if the step asked for both
                 g = self.group_of_step[i]
                 j = owners[g].index(i)

@@ -71,6 +71,119 @@ __global__ void qk_norm_rotary_store_kernel(T* __restrict__ q_out, const T* __re
   }
 }
 
+// The same with 16-byte accesses, for d % 8 == 0, rot % 16 == 0 and 16-byte aligned rows.  A work item is a run of
+// eight columns — together with its partner run, half the rotated span further, where it is rotated.  The token's
+// cosines and sines are computed once, in shared memory, not once per head.
+template <typename T>
+__global__ void qk_norm_rotary_store_vec_kernel(T* __restrict__ q_out, const T* __restrict__ proj, long long proj_stride,
+                                                const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                                                const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                                const int* __restrict__ slots, T* __restrict__ k_pool, T* __restrict__ v_pool, int nh,
+                                                int nkv, int d, int rot, int page_size, int write_kv, int normed, int values_from_keys) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float cs[];  // cos [rot / 2] | sin [rot / 2]
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int nq = nh * d, nk = nkv * d, half = rot >> 1;
+  const T* src = proj + (size_t)t * proj_stride;
+  const float pos = (float)positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &cs[half + j], &cs[j]);
+  float rq = 1.f, rk = 1.f;
+  if (normed) {
+    float sq = 0.f, sk = 0.f;
+    for (int e = threadIdx.x * 8; e < nq + nk; e += blockDim.x * 8) {
+      float x[8];
+      load8(src + e, x);
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss = fmaf(x[k], x[k], ss);
+      if (e < nq) sq += ss; else sk += ss;
+    }
+    rq = 1.f / sqrtf(block_sum(sq, red) / (float)nq + eps);
+    rk = 1.f / sqrtf(block_sum(sk, red) / (float)nk + eps);
+  } else {
+    __syncthreads();
+  }
+  long long kv_base = 0;
+  if (write_kv) {
+    const int slot = slots[t];
+    kv_base = ((long long)(slot / page_size) * nkv * page_size + slot % page_size) * d;
+  }
+  // items per head: half / 8 rotated pairs, then (d - rot) / 8 runs that pass unrotated
+  const int pair_items = half >> 3, per_head = pair_items + ((d - rot) >> 3);
+  const int heads = nh + (write_kv ? nkv : 0);
+  for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
+    const int head = item / per_head, it = item - head * per_head;
+    const bool is_q = head < nh;
+    const int hh = is_q ? head : head - nh;
+    const float r = is_q ? rq : rk;
+    const float* w = (is_q ? wq : wk) + hh * d;
+    const T* hsrc = src + head * d;  // q heads, then k heads, lie back to back
+    T* dst = is_q ? q_out + (size_t)t * nq + hh * d : k_pool + kv_base + (long long)hh * page_size * d;
+    T* vdst = is_q ? nullptr : v_pool + kv_base + (long long)hh * page_size * d;
+    const T* vsrc = values_from_keys ? hsrc : hsrc + nk;
+    if (it < pair_items) {
+      const int i = it * 8;
+      float lo[8], hi[8], wl[8], wh[8], ol[8], oh[8];
+      load8(hsrc + i, lo);
+      load8(hsrc + i + half, hi);
+      if (vdst) {
+        *reinterpret_cast<uint4*>(vdst + i) = *reinterpret_cast<const uint4*>(vsrc + i);
+        *reinterpret_cast<uint4*>(vdst + i + half) = *reinterpret_cast<const uint4*>(vsrc + i + half);
+        if (sizeof(T) == 4) {
+          *reinterpret_cast<uint4*>(vdst + i + 4) = *reinterpret_cast<const uint4*>(vsrc + i + 4);
+          *reinterpret_cast<uint4*>(vdst + i + half + 4) = *reinterpret_cast<const uint4*>(vsrc + i + half + 4);
+        }
+      }
+      if (normed) {
+        load8(w + i, wl);
+        load8(w + i + half, wh);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float a = lo[k] * r * (normed ? wl[k] : 1.f), b = hi[k] * r * (normed ? wh[k] : 1.f);
+        const float c = cs[i + k], sn = cs[half + i + k];
+        ol[k] = a * c - b * sn;
+        oh[k] = b * c + a * sn;
+      }
+      store8(dst + i, ol);
+      store8(dst + i + half, oh);
+    } else {
+      const int i = rot + (it - pair_items) * 8;
+      float x[8], wv[8];
+      load8(hsrc + i, x);
+      if (vdst) {
+        *reinterpret_cast<uint4*>(vdst + i) = *reinterpret_cast<const uint4*>(vsrc + i);
+        if (sizeof(T) == 4) *reinterpret_cast<uint4*>(vdst + i + 4) = *reinterpret_cast<const uint4*>(vsrc + i + 4);
+      }
+      if (normed) {
+        load8(w + i, wv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] = x[k] * r * wv[k];
+      }
+      store8(dst + i, x);
+    }
+  }
+}
+
+// out[t, c] *= sigmoid(gate[t, c]), eight columns a thread (cols % 8 == 0, aligned rows)
+template <typename T>
+__global__ void sigmoid_gate_vec_kernel(T* __restrict__ out, const T* __restrict__ gate, long long gate_stride, int n, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = cols >> 3;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * per_row) return;
+  const int t = (int)(idx / per_row), c = (int)(idx - (long long)t * per_row) * 8;
+  float o[8], g[8];
+  load8(out + (size_t)t * cols + c, o);
+  load8(gate + (size_t)t * gate_stride + c, g);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = o[k] / (1.f + expf(-g[k]));
+  store8(out + (size_t)t * cols + c, o);
+}
+
 // out[t, c] *= sigmoid(gate[t * gate_stride + c])
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ out, const T* __restrict__ gate, long long gate_stride, int n, int cols) {
@@ -96,6 +209,24 @@ DLI_EXPORT int dli_qk_norm_rotary_store(void* q_out, const void* proj, long long
     return DLI_ERR_UNSUPPORTED;
   const int threads = (nh + nkv) * d >= 2048 ? 512 : 256;
   cudaError_t e;
+  const size_t esize = dtype == DLI_F32 ? 4 : 2;
+  const bool aligned = (d % 8) == 0 && (rot % 16) == 0 && (proj_stride % 8) == 0 && rot * sizeof(float) <= 48 * 1024 &&
+                       (((uintptr_t)q_out | (uintptr_t)proj | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)wq | (uintptr_t)wk) & 15) == 0 &&
+                       ((size_t)d * esize) % 16 == 0;
+  if (aligned) {
+    const int items = (nh + nkv) * (d / 8);
+    const int vt = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+    const size_t vsmem = (size_t)rot * sizeof(float);
+    if (dtype == DLI_F32)
+      e = launch_pdl((qk_norm_rotary_store_vec_kernel<float>), dim3(n), dim3(vt), vsmem, stream, 1, (float*)q_out, (const float*)proj,
+                     proj_stride, wq, wk, eps, positions, inv_freq, slots, (float*)k_pool, (float*)v_pool, nh, nkv, d, rot, page_size,
+                     write_kv, normed, values_from_keys);
+    else
+      e = launch_pdl((qk_norm_rotary_store_vec_kernel<__nv_bfloat16>), dim3(n), dim3(vt), vsmem, stream, 1, (__nv_bfloat16*)q_out,
+                     (const __nv_bfloat16*)proj, proj_stride, wq, wk, eps, positions, inv_freq, slots, (__nv_bfloat16*)k_pool,
+                     (__nv_bfloat16*)v_pool, nh, nkv, d, rot, page_size, write_kv, normed, values_from_keys);
+    return (int)e;
+  }
   if (dtype == DLI_F32) {
     static MaxPerDevice set;
     if ((int)smem > 48 * 1024 && set.here() < (int)smem) {
@@ -123,8 +254,17 @@ DLI_EXPORT int dli_qk_norm_rotary_store(void* q_out, const void* proj, long long
 DLI_EXPORT int dli_sigmoid_gate(void* out, const void* gate, long long gate_stride, int n, int cols, int dtype, cudaStream_t stream) {
   if (n == 0 || cols == 0) return 0;
   const long long total = (long long)n * cols;
-  const int blocks = (int)((total + 255) / 256);
   cudaError_t e;
+  if ((cols % 8) == 0 && (gate_stride % 8) == 0 && (((uintptr_t)out | (uintptr_t)gate) & 15) == 0) {
+    const int vblocks = (int)((total / 8 + 255) / 256);
+    if (dtype == DLI_F32)
+      e = launch_pdl((sigmoid_gate_vec_kernel<float>), dim3(vblocks), dim3(256), 0, stream, 1, (float*)out, (const float*)gate, gate_stride, n, cols);
+    else
+      e = launch_pdl((sigmoid_gate_vec_kernel<__nv_bfloat16>), dim3(vblocks), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)gate, gate_stride, n, cols);
+    return (int)e;
+  }
+  const int blocks = (int)((total + 255) / 256);
   if (dtype == DLI_F32)
     e = launch_pdl((sigmoid_gate_kernel<float>), dim3(blocks), dim3(256), 0, stream, 1, (float*)out, (const float*)gate, gate_stride, n, cols);
   else

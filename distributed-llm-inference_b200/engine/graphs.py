@@ -43,8 +43,9 @@ class DecodeGraph:
     """One captured shape: ``seqs`` rows, tables ``width`` pages wide."""
 
     def __init__(self, model, caches, num_groups: int, scratch_pages: list[int], page_size: int, seqs: int, width: int,
-                 launch_keys: dict) -> None:
+                 launch_keys: dict, scratch_state_slot: int = 0) -> None:
         self.seqs, self.width, self.num_groups = seqs, width, num_groups
+        self.scratch_state_slot = scratch_state_slot  # the state slot of padding rows: one no request owns
         dev = model.device
         per_group = seqs + seqs * width
         self.src_base = 4 * seqs + num_groups * per_group  # behind the groups: each row's place in the token source, or -1
@@ -85,6 +86,7 @@ class DecodeGraph:
         seqs, width = self.seqs, self.width
         flat = np.zeros(self.size, dtype=np.int32)
         flat[2 * seqs : 3 * seqs] = 1  # kv_len
+        flat[3 * seqs : 4 * seqs] = self.scratch_state_slot
         per_group = seqs + seqs * width
         for g, page in enumerate(scratch_pages):
             base = 4 * seqs + g * per_group
@@ -132,7 +134,8 @@ class MixedGraph:
     the singles' first, then the portions' back to back, then padding."""
 
     def __init__(self, model, caches, num_groups: int, scratch_pages: list[int], page_size: int, singles: int, portions: int,
-                 tokens: int, width: int, launch_keys: dict, pool=None) -> None:
+                 tokens: int, width: int, launch_keys: dict, pool=None, scratch_state_slot: int = 0) -> None:
+        self.scratch_state_slot = scratch_state_slot
         self.set_layout(singles, portions, tokens, width, num_groups)
         dev = model.device
         self._pad = self.padding(scratch_pages, page_size)
@@ -186,6 +189,7 @@ class MixedGraph:
         flat[o["q_start"] : o["q_start"] + singles + 1] = np.arange(singles + 1)
         flat[o["q_start"] + singles + 1 : o["q_start"] + S + 1] = singles
         flat[o["kv_len"] : o["kv_len"] + S] = 1
+        flat[o["state_slot"] : o["state_slot"] + S] = getattr(self, "scratch_state_slot", 0)
         for g, page in enumerate(scratch_pages):
             base = o["groups"] + g * self.per_group
             flat[base : base + n] = page * page_size
@@ -293,7 +297,8 @@ class DecodeGraphs:
                 del self.graphs[next(iter(self.graphs))]  # shapes drift in a long run: the stalest graph goes
             try:
                 graph = self.graphs[key] = DecodeGraph(self.model, self.pools.layer_caches, len(self.pools.group_needs),
-                                                       self.pools.scratch_pages, self.page_size, seqs, width, launch)
+                                                       self.pools.scratch_pages, self.page_size, seqs, width, launch,
+                                                       scratch_state_slot=self.pools.scratch_state_slot)
             except RuntimeError as exc:  # a part turned out not to be capturable after all: run step by step from now on
                 self.max_graphs = 0
                 self.failure = str(exc)
@@ -334,7 +339,8 @@ class DecodeGraphs:
         began = time.perf_counter()
         try:
             graph = self.mixed[key] = MixedGraph(self.model, self.pools.layer_caches, len(self.pools.group_needs), self.pools.scratch_pages,
-                                                 self.page_size, sb, pb, tb, wb, launch, self._pool)
+                                                 self.page_size, sb, pb, tb, wb, launch, self._pool,
+                                                 scratch_state_slot=self.pools.scratch_state_slot)
             self.mixed_captures += 1
             self.mixed_capture_seconds += time.perf_counter() - began
         except RuntimeError as exc:  # no memory for it, or a part that cannot be captured with longer portions: these steps stay uncaptured

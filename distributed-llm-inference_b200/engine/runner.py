@@ -88,9 +88,9 @@ class ModelRunner:
         )
         self.page_size = page_size
         self.uploader = Uploader(model.device)
-        # graphs replay padding rows through every mixer: not with per-request state, which they would touch
+        # graphs replay padding rows through every mixer; those rows name a state slot of their own (pools.scratch_state_slot)
         capturable = all(getattr(part, "graph_capturable", False) for part in model.parts())
-        self.graphs = DecodeGraphs(model, self.pools, page_size) if cuda_graphs and capturable and not self.pools.has_state else None
+        self.graphs = DecodeGraphs(model, self.pools, page_size) if cuda_graphs and capturable else None
         self.graph_steps = 0  # pure-decode steps replayed from a graph
         self.mixed_graph_steps = 0  # small steps with prompt portions replayed from a graph
 

@@ -956,14 +956,14 @@ SSM_SCAN_MAX_STATE = 256
 
 def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, groups: int) -> None:
-    """The selective scan of every sequence's tokens of this step, from and to its slot of ``state`` [slots, heads, N, P]
-    (float32).  xbc [n, heads P + 2 groups N] holds x | B | C; dt_raw is column dt_col + head of u.  Per head:
+    """The selective scan of every sequence's tokens of this step, from and to its slot of ``state`` [slots, heads, P, N]
+    (float32; S transposed, so that a column's N values are contiguous).  xbc [n, heads P + 2 groups N] holds x | B | C; dt_raw is column dt_col + head of u.  Per head:
     dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d_skip x.  y [n, heads P] float32."""
     _columns(u, "ssm_scan"), _need(xbc, "xbc", u.dtype), _need(y, "y", torch.float32), _need(state, "state", torch.float32)
     for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
         _need(t, name, torch.float32)
     _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
-    _, heads, N, P = state.shape
+    _, heads, P, N = state.shape
     n = xbc.shape[0]
     if (xbc.shape[1] != heads * P + 2 * groups * N or tuple(y.shape) != (n, heads * P) or u.shape[0] != n or dt_col + heads > u.shape[1]
             or heads % groups or N > SSM_SCAN_MAX_STATE or dt_bias.numel() != heads or a_log.numel() != heads or d_skip.numel() != heads

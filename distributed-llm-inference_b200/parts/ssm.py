@@ -19,7 +19,7 @@ class Mamba2Mixer(Part):
     groups * state_size each for B and C, one dt per head).  x | B | C pass a causal convolution per channel
     (``conv_taps`` taps, bias) and SiLU.  Per head, with dt = softplus(dt + dt_bias) and its group's B and C:
 
-        S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T        (S: state_size x head_dim, float32)
+        S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T        (S: state_size x head_dim, float32; kept transposed)
         y_t = S_t^T C_t + D x_t
 
     y * silu(z) is divided by its RMS in ``norm_groups`` equal parts of the row, multiplied by a weight, and goes
@@ -29,7 +29,7 @@ class Mamba2Mixer(Part):
     params: hidden_size, num_heads, head_dim, state_size, groups, conv_taps, norm_groups, eps, tensors (names of
     in, conv, conv_bias, dt_bias, A_log, D, norm, o)."""
 
-    graph_capturable = False  # padding rows of a replayed graph would touch a state slot
+    graph_capturable = True  # padding rows of a replayed graph name a state slot that no request owns
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
@@ -67,7 +67,7 @@ class Mamba2Mixer(Part):
 
     def cache_need(self):
         """The recurrent state (float32) and the convolution's carried inputs (activation dtype), per request."""
-        return (StateNeed((self.heads, self.N, self.P), torch.float32), StateNeed((self.taps - 1, self.channels), self.env.dtype))
+        return (StateNeed((self.heads, self.P, self.N), torch.float32), StateNeed((self.taps - 1, self.channels), self.env.dtype))
 
     def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
         w = self.w

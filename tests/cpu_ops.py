@@ -234,7 +234,7 @@ def conv_state_update(state, u, col0, q_start, state_slot):
 
 
 def ssm_scan(y, xbc, u, dt_col, dt_bias, a_log, d_skip, state, q_start, state_slot, groups):
-    _, heads, N, P = state.shape
+    _, heads, P, N = state.shape  # the state is kept transposed: [slot, head, p, n]
     inner = heads * P
     for s in range(state_slot.numel()):
         slot = int(state_slot[s])
@@ -244,8 +244,8 @@ def ssm_scan(y, xbc, u, dt_col, dt_bias, a_log, d_skip, state, q_start, state_sl
             C = xbc[t, inner + groups * N :].float().view(groups, N).repeat_interleave(heads // groups, 0)
             dt = torch.nn.functional.softplus(u[t, dt_col : dt_col + heads].float() + dt_bias, threshold=20.0)
             decay = torch.exp(-torch.exp(a_log) * dt)
-            state[slot] = decay[:, None, None] * state[slot] + (dt[:, None] * B)[:, :, None] * x[:, None, :]
-            y[t] = (torch.einsum("hnp,hn->hp", state[slot], C) + d_skip[:, None] * x).reshape(-1)
+            state[slot] = decay[:, None, None] * state[slot] + x[:, :, None] * (dt[:, None] * B)[:, None, :]
+            y[t] = (torch.einsum("hpn,hn->hp", state[slot], C) + d_skip[:, None] * x).reshape(-1)
 
 
 def gated_group_rmsnorm(out, y, u, z_col, weight, parts, eps):

@@ -26,7 +26,7 @@ def _close(got, want, tol, what=""):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("H", [40, 256, 1000, 4096])
+@pytest.mark.parametrize("H", [40, 77, 256, 1000, 4096, 8200])
 def test_post_add_layernorm(dtype, tol, H):
     n = 7
     h = _rand(n, H, seed=1) * 3 + 0.5
@@ -72,9 +72,9 @@ def test_stream_reinject_and_activation(dtype, tol):
 @pytest.mark.parametrize("dtype,tol", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,rot,normed,from_keys", [(4, 2, 16, 16, True, True), (3, 1, 32, 8, True, True), (8, 8, 64, 0, False, False),
                                                             (6, 2, 48, 48, True, False), (16, 2, 128, 64, True, True)])
-def test_qk_norm_rotary_store(dtype, tol, nh, nkv, d, rot, normed, from_keys):
+@pytest.mark.parametrize("extra", [13, 16])  # columns behind q | k (| v): rows that are and are not 16-byte aligned
+def test_qk_norm_rotary_store(dtype, tol, nh, nkv, d, rot, normed, from_keys, extra):
     n, page, pages = 9, 8, 5
-    extra = 13
     cols = (nh + (1 if from_keys else 2) * nkv) * d + extra
     proj = _rand(n, cols, seed=1).to(dtype)
     wq, wk = (1 + 0.2 * _rand(nh * d, seed=2), 1 + 0.2 * _rand(nkv * d, seed=3)) if normed else (None, None)
@@ -95,13 +95,14 @@ def test_qk_norm_rotary_store(dtype, tol, nh, nkv, d, rot, normed, from_keys):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-def test_sigmoid_gate(dtype, tol):
+@pytest.mark.parametrize("width,lo", [(100, 50), (104, 48)])
+def test_sigmoid_gate(dtype, tol, width, lo):
     out = _rand(6, 40, seed=1).to(dtype)
-    wide = (_rand(6, 100, seed=2) * 4).to(dtype)
+    wide = (_rand(6, width, seed=2) * 4).to(dtype)
     want = out.clone()
-    ref.sigmoid_gate(want, wide[:, 50:90])
+    ref.sigmoid_gate(want, wide[:, lo : lo + 40])
     got = out.cuda()
-    ops.sigmoid_gate(got, wide.cuda()[:, 50:90])
+    ops.sigmoid_gate(got, wide.cuda()[:, lo : lo + 40])
     _close(got, want, tol)
 
 
@@ -115,13 +116,14 @@ def _batch(q_lens):
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
 @pytest.mark.parametrize("taps", [1, 2, 4])
-def test_causal_conv_and_its_state(dtype, tol, taps):
-    C, col0, slots = 150, 11, 6
+@pytest.mark.parametrize("C,col0", [(150, 11), (152, 8), (2304, 16)])
+def test_causal_conv_and_its_state(dtype, tol, taps, C, col0):
+    slots = 6
     q_lens = [1, 5, 2, 1]
     q_start, seq_of = _batch(q_lens)
     n = int(q_start[-1])
     slot = torch.tensor([4, 0, 5, 2], dtype=torch.int32)
-    u = _rand(n, col0 + C + 3, seed=1).to(dtype)
+    u = _rand(n, col0 + C + (3 if C % 8 else 8), seed=1).to(dtype)
     w, b = _rand(C, taps, seed=2), _rand(C, seed=3)
     state = _rand(slots, taps - 1, C, seed=4).to(dtype)
     out_ref, out = torch.empty(n, C, dtype=dtype), torch.empty(n, C, dtype=dtype, device="cuda")
@@ -136,9 +138,9 @@ def test_causal_conv_and_its_state(dtype, tol, taps):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("heads,P,N,groups", [(6, 48, 32, 2), (4, 64, 128, 1), (3, 20, 10, 3), (2, 96, 256, 2), (8, 8, 64, 4)])
+@pytest.mark.parametrize("heads,P,N,groups", [(6, 48, 32, 2), (4, 64, 128, 1), (3, 20, 10, 3), (2, 96, 256, 2), (8, 8, 64, 4), (1, 5, 33, 1)])
 def test_ssm_scan(dtype, tol, heads, P, N, groups):
-    q_lens = [1, 37, 2, 1]
+    q_lens = [1, 77, 2, 32]
     q_start, _ = _batch(q_lens)
     n = int(q_start[-1])
     slot = torch.tensor([3, 1, 0, 4], dtype=torch.int32)
@@ -147,7 +149,7 @@ def test_ssm_scan(dtype, tol, heads, P, N, groups):
     dt_col = 5
     u = _rand(n, dt_col + heads + 2, seed=2).to(dtype)
     dt_bias, a_log, d_skip = _rand(heads, seed=3), _rand(heads, seed=4) * 0.5, _rand(heads, seed=5)
-    state = _rand(5, heads, N, P, seed=6)
+    state = _rand(5, heads, P, N, seed=6)
     y_ref, y = torch.zeros(n, inner), torch.zeros(n, inner, device="cuda")
     st_ref, st = state.clone(), state.cuda()
     ref.ssm_scan(y_ref, xbc, u, dt_col, dt_bias, a_log, d_skip, st_ref, q_start, slot, groups)
@@ -157,11 +159,11 @@ def test_ssm_scan(dtype, tol, heads, P, N, groups):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("inner,parts", [(288, 2), (64, 1), (120, 5), (4096, 8)])
+@pytest.mark.parametrize("inner,parts", [(288, 2), (64, 1), (120, 5), (90, 3), (4096, 8), (16384, 1)])
 def test_gated_group_rmsnorm(dtype, tol, inner, parts):
-    n, z_col = 5, 3
+    n, z_col = 5, (3 if inner == 90 else 8)
     y = _rand(n, inner, seed=1) * 2
-    u = _rand(n, z_col + inner + 4, seed=2).to(dtype)
+    u = _rand(n, z_col + inner + (4 if inner == 90 else 8), seed=2).to(dtype)
     w = 1 + 0.1 * _rand(inner, seed=3)
     out_ref, out = torch.empty(n, inner, dtype=dtype), torch.empty(n, inner, dtype=dtype, device="cuda")
     ref.gated_group_rmsnorm(out_ref, y, u, z_col, w, parts, 1e-6)
