@@ -510,14 +510,14 @@ def design_kernels(size, pk, tokens=4096, seqs=64):
         # state-space mixer
         u = torch.randn(n, inner + C + Hs, device=dev).to(bf)
         xbc = torch.empty(n, C, dtype=bf, device=dev)
-        cw, cb = torch.randn(C, taps, device=dev), torch.randn(C, device=dev)
+        cw, cb = torch.randn(taps, C, device=dev), torch.randn(C, device=dev)
         cstate = torch.zeros(S, taps - 1, C, dtype=bf, device=dev)
         record(f"{label}.causal_conv_silu", time_kernel(lambda: ops.causal_conv_silu(xbc, u, inner, cw, cb, cstate, seq_of, q_start, slot)),
                n * C * 4 + (S * (taps - 1) * C * 2 if S > 1 else 0), "silu_mul")
         state = torch.zeros(S, Hs, P, N, device=dev)
         ys = torch.empty(n, inner, device=dev)
         dtb, al, dk = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
-        scan_us = time_kernel(lambda: ops.ssm_scan(ys, xbc, u, inner + C, dtb, al, dk, state, q_start, slot, G))
+        scan_us = time_kernel(lambda: ops.ssm_scan(ys, xbc, u, inner + C, dtb, al, dk, state, q_start, slot, G, max_len=n // S))
         scan_bytes = S * Hs * N * P * 8 + n * (C * 2 + inner * 4)
         record(f"{label}.ssm_scan", scan_us, scan_bytes, "decode attention" if S > 1 else "prefill attention", flops=5.0 * n * Hs * N * P)
         gated = torch.empty(n, inner, dtype=bf, device=dev)

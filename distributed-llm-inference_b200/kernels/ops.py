@@ -923,14 +923,15 @@ def _columns(u: torch.Tensor, name: str) -> None:
 
 def causal_conv_silu(out: torch.Tensor, u: torch.Tensor, col0: int, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
                      seq_of_token: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor) -> None:
-    """out[t, c] = silu(bias[c] + sum_j weight[c, j] * in(t - (taps - 1) + j, c)) for channels c = columns col0 .. of u.
+    """out[t, c] = silu(bias[c] + sum_j weight[j, c] * in(t - (taps - 1) + j, c)) for channels c = columns col0 .. of u
+    (``weight`` [taps, C]: each tap's weights lie together).
     The last tap weighs the token itself; in() before the step's first token of a sequence is the sequence's carried
     input in ``state`` [slots, taps - 1, C] (oldest first).  ``conv_state_update`` moves the state on afterwards."""
     _columns(u, "causal_conv_silu"), _need(out, "out", u.dtype), _need(weight, "weight", torch.float32), _need(state, "state", u.dtype)
     _need(seq_of_token, "seq_of_token", torch.int32), _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
     n, C = out.shape
-    taps = weight.shape[1]
-    if u.shape[0] != n or col0 + C > u.shape[1] or weight.shape[0] != C or tuple(state.shape[1:]) != (taps - 1, C) or seq_of_token.numel() != n:
+    taps = weight.shape[0]
+    if u.shape[0] != n or col0 + C > u.shape[1] or weight.shape[1] != C or tuple(state.shape[1:]) != (taps - 1, C) or seq_of_token.numel() != n:
         raise KernelError("causal_conv_silu: shapes do not agree")
     if bias is not None:
         _need(bias, "bias", torch.float32)
@@ -955,10 +956,11 @@ SSM_SCAN_MAX_STATE = 256
 
 
 def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
-             state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, groups: int) -> None:
+             state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, groups: int, max_len: int = 1 << 30) -> None:
     """The selective scan of every sequence's tokens of this step, from and to its slot of ``state`` [slots, heads, P, N]
     (float32; S transposed, so that a column's N values are contiguous).  xbc [n, heads P + 2 groups N] holds x | B | C; dt_raw is column dt_col + head of u.  Per head:
-    dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d_skip x.  y [n, heads P] float32."""
+    dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d_skip x.  y [n, heads P] float32.
+    ``max_len``: the most tokens a sequence brings, if the host knows (a launch hint: nothing is fetched ahead for single tokens)."""
     _columns(u, "ssm_scan"), _need(xbc, "xbc", u.dtype), _need(y, "y", torch.float32), _need(state, "state", torch.float32)
     for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
         _need(t, name, torch.float32)
@@ -970,9 +972,9 @@ def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, d
             or q_start.numel() != state_slot.numel() + 1):
         raise KernelError("ssm_scan: shapes do not agree (or the state size is above 256)")
     f = _fn("ssm.cu", "dli_ssm_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
-            + [c_int] * 6 + [c_void_p])
+            + [c_int] * 7 + [c_void_p])
     _check(f(_ptr(y), _ptr(xbc), _ptr(u), u.stride(0), dt_col, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(q_start),
-             _ptr(state_slot), state_slot.numel(), heads, P, N, groups, DT_CODE[u.dtype], _stream()), "ssm_scan")
+             _ptr(state_slot), state_slot.numel(), heads, P, N, groups, int(max_len), DT_CODE[u.dtype], _stream()), "ssm_scan")
 
 
 def gated_group_rmsnorm(out: torch.Tensor, y: torch.Tensor, u: torch.Tensor, z_col: int, weight: torch.Tensor, parts: int, eps: float) -> None:

@@ -64,6 +64,7 @@ class Mamba2Mixer(Part):
 
     def load(self, tensors):
         self.w = {role: tensors[name] for role, name in self.names.items()}
+        self.w["conv"] = self.w["conv"].t().contiguous()  # [taps, channels]: the kernel reads a tap's weights side by side
 
     def cache_need(self):
         """The recurrent state (float32) and the convolution's carried inputs (activation dtype), per request."""
@@ -80,7 +81,7 @@ class Mamba2Mixer(Part):
             ops.conv_state_update(conv_state, u, self.inner, batch.q_start, batch.state_slot)
         y = torch.empty((n, self.inner), dtype=torch.float32, device=x.device)
         ops.ssm_scan(y, xbc, u, self.inner + self.channels, w["dt_bias"], w["A_log"], w["D"], ssm_state, batch.q_start, batch.state_slot,
-                     self.groups)
+                     self.groups, max_len=batch.max_q_len)
         gated = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         ops.gated_group_rmsnorm(gated, y, u, 0, w["norm"], self.parts, self.eps)
         return project(gated, w["o"])

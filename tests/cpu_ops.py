@@ -213,7 +213,7 @@ def _silu(x):
 
 def causal_conv_silu(out, u, col0, weight, bias, state, seq_of_token, q_start, state_slot):
     n, C = out.shape
-    taps = weight.shape[1]
+    taps = weight.shape[0]  # weight [taps, C]
     for t in range(n):
         s = int(seq_of_token[t])
         first, slot = int(q_start[s]), int(state_slot[s])
@@ -221,7 +221,7 @@ def causal_conv_silu(out, u, col0, weight, bias, state, seq_of_token, q_start, s
         for j in range(taps):
             r = t - first - (taps - 1) + j
             x = u[first + r, col0 : col0 + C] if r >= 0 else state[slot, taps - 1 + r]
-            acc = acc + weight[:, j] * x.float()
+            acc = acc + weight[j] * x.float()
         out[t] = _silu(acc).to(out.dtype)
 
 
@@ -233,7 +233,7 @@ def conv_state_update(state, u, col0, q_start, state_slot):
         state[slot] = seen[seen.shape[0] - keep :]
 
 
-def ssm_scan(y, xbc, u, dt_col, dt_bias, a_log, d_skip, state, q_start, state_slot, groups):
+def ssm_scan(y, xbc, u, dt_col, dt_bias, a_log, d_skip, state, q_start, state_slot, groups, max_len=0):
     _, heads, P, N = state.shape  # the state is kept transposed: [slot, head, p, n]
     inner = heads * P
     for s in range(state_slot.numel()):

@@ -124,7 +124,7 @@ def test_causal_conv_and_its_state(dtype, tol, taps, C, col0):
     n = int(q_start[-1])
     slot = torch.tensor([4, 0, 5, 2], dtype=torch.int32)
     u = _rand(n, col0 + C + (3 if C % 8 else 8), seed=1).to(dtype)
-    w, b = _rand(C, taps, seed=2), _rand(C, seed=3)
+    w, b = _rand(taps, C, seed=2), _rand(C, seed=3)
     state = _rand(slots, taps - 1, C, seed=4).to(dtype)
     out_ref, out = torch.empty(n, C, dtype=dtype), torch.empty(n, C, dtype=dtype, device="cuda")
     st_ref, st = state.clone(), state.cuda()
@@ -138,7 +138,7 @@ def test_causal_conv_and_its_state(dtype, tol, taps, C, col0):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("heads,P,N,groups", [(6, 48, 32, 2), (4, 64, 128, 1), (3, 20, 10, 3), (2, 96, 256, 2), (8, 8, 64, 4), (1, 5, 33, 1)])
+@pytest.mark.parametrize("heads,P,N,groups", [(6, 48, 32, 2), (4, 64, 128, 1), (3, 20, 10, 3), (2, 96, 256, 2), (8, 8, 64, 4), (1, 5, 33, 1), (160, 40, 24, 8)])
 def test_ssm_scan(dtype, tol, heads, P, N, groups):
     q_lens = [1, 77, 2, 32]
     q_start, _ = _batch(q_lens)
@@ -155,6 +155,10 @@ def test_ssm_scan(dtype, tol, heads, P, N, groups):
     ref.ssm_scan(y_ref, xbc, u, dt_col, dt_bias, a_log, d_skip, st_ref, q_start, slot, groups)
     ops.ssm_scan(y, xbc.cuda(), u.cuda(), dt_col, dt_bias.cuda(), a_log.cuda(), d_skip.cuda(), st, q_start.cuda(), slot.cuda(), groups)
     _close(y, y_ref, 1e-4, "y"), _close(st, st_ref, 1e-4, "state")
+    # the launch for steps of single tokens (nothing fetched ahead) computes the same
+    y2, st2 = torch.zeros(n, inner, device="cuda"), state.cuda()
+    ops.ssm_scan(y2, xbc.cuda(), u.cuda(), dt_col, dt_bias.cuda(), a_log.cuda(), d_skip.cuda(), st2, q_start.cuda(), slot.cuda(), groups, max_len=1)
+    _close(y2, y_ref, 1e-4, "y, no prefetch"), _close(st2, st_ref, 1e-4, "state, no prefetch")
     assert torch.equal(st[2].cpu(), state[2]), "a slot of no sequence was touched"
 
 
