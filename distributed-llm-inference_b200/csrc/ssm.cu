@@ -38,17 +38,19 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
   out[(size_t)t * C + c] = from_float<T>(silu(acc));
 }
 
-// The same, eight channels a thread with 16-byte accesses (C, col0 and the row strides multiples of 8, at most 8 taps).
+// The same, eight channels a thread with 16-byte accesses (C, col0 and the row strides multiples of 8).  A block takes
+// eight consecutive tokens of a slab of channels (threadIdx.y), so the rows that neighbouring tokens share are read
+// from L1, not again from L2.
 template <typename T>
 __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __restrict__ u, long long u_stride, int col0,
                                             const float* __restrict__ w, const float* __restrict__ bias, const T* __restrict__ state,
                                             const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-                                            const int* __restrict__ state_slot, int C, int taps) {
+                                            const int* __restrict__ state_slot, int n, int C, int taps) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
-  if (c >= C) return;
-  const int t = blockIdx.x;
+  const int t = blockIdx.x * blockDim.y + threadIdx.y;
+  if (c >= C || t >= n) return;
   const int s = seq_of_token[t];
   const int first = q_start[s];
   const int r0 = t - first;
@@ -448,14 +450,14 @@ DLI_EXPORT int dli_causal_conv_silu(void* out, const void* u, long long u_stride
   if (C < 1 || taps < 1 || (C + 127) / 128 > 65535) return DLI_ERR_UNSUPPORTED;
   cudaError_t e;
   if ((C % 8) == 0 && (col0 % 8) == 0 && (u_stride % 8) == 0 && (((uintptr_t)out | (uintptr_t)u | (uintptr_t)state | (uintptr_t)bias | (uintptr_t)w) & 15) == 0) {
-    const int items = C / 8, vt = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
-    const dim3 vgrid(n, (items + vt - 1) / vt);
+    const int items = C / 8;
+    const dim3 vblock(32, 8), vgrid((n + 7) / 8, (items + 31) / 32);
     if (dtype == DLI_F32)
-      e = launch_pdl((causal_conv_silu_vec_kernel<float>), vgrid, dim3(vt), 0, stream, 1, (float*)out, (const float*)u, u_stride, col0, w, bias,
-                     (const float*)state, seq_of_token, q_start, state_slot, C, taps);
+      e = launch_pdl((causal_conv_silu_vec_kernel<float>), vgrid, vblock, 0, stream, 1, (float*)out, (const float*)u, u_stride, col0, w, bias,
+                     (const float*)state, seq_of_token, q_start, state_slot, n, C, taps);
     else
-      e = launch_pdl((causal_conv_silu_vec_kernel<__nv_bfloat16>), vgrid, dim3(vt), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)u,
-                     u_stride, col0, w, bias, (const __nv_bfloat16*)state, seq_of_token, q_start, state_slot, C, taps);
+      e = launch_pdl((causal_conv_silu_vec_kernel<__nv_bfloat16>), vgrid, vblock, 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)u,
+                     u_stride, col0, w, bias, (const __nv_bfloat16*)state, seq_of_token, q_start, state_slot, n, C, taps);
     return (int)e;
   }
   const dim3 grid(n, (C + 127) / 128), block(128);
