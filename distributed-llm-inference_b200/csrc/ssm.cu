@@ -9,6 +9,9 @@ using namespace dli;
 namespace {
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
+// for outputs that are rounded to bfloat16 anyway: the fast exponential and division (a few ulp of float32)
+template <typename T> __device__ __forceinline__ float silu_out(float x) { return silu(x); }
+template <> __device__ __forceinline__ float silu_out<__nv_bfloat16>(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // out[t, c] = silu(bias[c] + sum_j w[j, c] * in(t - (taps - 1) + j, c)) (w [taps, C]: a tap's weights are contiguous);
@@ -35,7 +38,7 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
     const float x = r >= 0 ? to_float(u[(size_t)(first + r) * u_stride + col0 + c]) : to_float(carried[(size_t)(taps - 1 + r) * C + c]);
     acc = fmaf(w[(size_t)j * C + c], x, acc);
   }
-  out[(size_t)t * C + c] = from_float<T>(silu(acc));
+  out[(size_t)t * C + c] = from_float<T>(silu_out<T>(acc));
 }
 
 // The same, eight channels a thread with 16-byte accesses (C, col0 and the row strides multiples of 8).  A block takes
@@ -72,7 +75,7 @@ __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __rest
     for (int k = 0; k < 8; ++k) acc[k] = fmaf(wv[k], x[k], acc[k]);
   }
 #pragma unroll
-  for (int k = 0; k < 8; ++k) acc[k] = silu(acc[k]);
+  for (int k = 0; k < 8; ++k) acc[k] = silu_out<T>(acc[k]);
   store8(out + (size_t)t * C + c, acc);
 }
 

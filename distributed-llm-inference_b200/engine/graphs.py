@@ -86,7 +86,7 @@ class DecodeGraph:
         seqs, width = self.seqs, self.width
         flat = np.zeros(self.size, dtype=np.int32)
         flat[2 * seqs : 3 * seqs] = 1  # kv_len
-        flat[3 * seqs : 4 * seqs] = self.scratch_state_slot
+        flat[3 * seqs : 4 * seqs] = getattr(self, "scratch_state_slot", 0)
         per_group = seqs + seqs * width
         for g, page in enumerate(scratch_pages):
             base = 4 * seqs + g * per_group

@@ -39,6 +39,24 @@ def test_padding_rows_live_in_the_scratch_page():
     assert flat[g.src_base :].tolist() == [-1] * 4  # no row takes its token from the device
 
 
+def test_padding_rows_name_a_state_slot_of_their_own():
+    """With mixers that keep per-request state, a graph's padding rows use the slot behind the last one a request can
+    own (the pools allocate one slot more): a replay leaves every live request's state alone."""
+    g = DecodeGraph.__new__(DecodeGraph)
+    g.seqs, g.width, g.num_groups, g.scratch_state_slot = 4, 8, 1, 6
+    g.src_base = 4 * 4 + (4 + 4 * 8)
+    g.size = g.src_base + 4
+    assert g.padding([9], 16)[12:16].tolist() == [6] * 4
+    import torch
+
+    from dli_b200.cache.needs import StateNeed
+    from dli_b200.cache.pools import CachePools
+    from dli_b200.config.spec import RunStep
+
+    pools = CachePools([StateNeed((2, 3))], [RunStep(0)], [], 16, 6, torch.float32, "cpu")
+    assert pools.scratch_state_slot == 6 and pools.layer_caches[0].state.shape == (7, 2, 3)
+
+
 def test_fill_puts_a_gathered_step_in_front_of_the_padding():
     m = CacheManager([GroupSpec(64), GroupSpec(64)], 16, 8, enable_prefix_caching=False, watermark=0.0)
     entries = []
@@ -73,7 +91,7 @@ def test_graphs_are_keyed_by_what_the_parts_answer_and_the_stalest_one_makes_roo
     made = []
 
     class Recorded:
-        def __init__(self, model, caches, num_groups, scratch_pages, page_size, seqs, width, launch_keys):
+        def __init__(self, model, caches, num_groups, scratch_pages, page_size, seqs, width, launch_keys, scratch_state_slot=0):
             self.shape, self.launch_keys = (seqs, width), dict(launch_keys)
             made.append(self)
 
@@ -92,7 +110,7 @@ def test_graphs_are_keyed_by_what_the_parts_answer_and_the_stalest_one_makes_roo
 
     a, b = Splitter(), Splitter()
     model = SimpleNamespace(parts=lambda: [a, Indifferent(), Unaware(), b], device="cpu")
-    pools = SimpleNamespace(layer_caches=[], group_needs=[None], scratch_pages=[7])
+    pools = SimpleNamespace(layer_caches=[], group_needs=[None], scratch_pages=[7], scratch_state_slot=0)
     graphs = DecodeGraphs(model, pools, page_size=16)
     g1 = graphs.lookup(3, 10, 150)  # 4 rows, 64 pages = 1,024 keys
     assert g1.shape == (4, 64) and g1.launch_keys == {id(a): 1, id(b): 1} and list(graphs.graphs) == [(4, 64, (1, 1))]
@@ -165,14 +183,15 @@ def test_mixed_shapes_are_captured_when_they_keep_coming_and_thrashing_shapes_wa
     made = []
 
     class Recorded:
-        def __init__(self, model, caches, num_groups, scratch_pages, page_size, singles, portions, tokens, width, launch_keys, pool=None):
+        def __init__(self, model, caches, num_groups, scratch_pages, page_size, singles, portions, tokens, width, launch_keys, pool=None,
+                     scratch_state_slot=0):
             self.shape = (singles, portions, tokens, width)
             made.append(self.shape)
 
     monkeypatch.setattr(graphs_mod, "MixedGraph", Recorded)
     monkeypatch.setattr(graphs_mod.torch.cuda, "graph_pool_handle", lambda: "pool")
     model = SimpleNamespace(parts=lambda: [], device="cpu")
-    pools = SimpleNamespace(layer_caches=[], group_needs=[None], scratch_pages=[7])
+    pools = SimpleNamespace(layer_caches=[], group_needs=[None], scratch_pages=[7], scratch_state_slot=0)
     graphs = DecodeGraphs(model, pools, page_size=16)
     assert graphs.mixed_after >= 8  # a capture costs many steps
     graphs.mixed_after = 2
