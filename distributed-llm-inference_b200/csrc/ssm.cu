@@ -79,6 +79,74 @@ __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __rest
   store8(out + (size_t)t * C + c, acc);
 }
 
+// For 2 to 4 taps: a thread takes eight channels of CONV_TOKS consecutive tokens, keeps the taps' weights and the last
+// TAPS - 1 inputs in registers and reads one new row per token (the window is read anew where a sequence begins).
+constexpr int CONV_TOKS = 8;
+
+template <typename T, int TAPS>
+__global__ void causal_conv_silu_window_kernel(T* __restrict__ out, const T* __restrict__ u, long long u_stride, int col0,
+                                               const float* __restrict__ w, const float* __restrict__ bias, const T* __restrict__ state,
+                                               const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
+                                               const int* __restrict__ state_slot, int n, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int t0 = blockIdx.x * CONV_TOKS;
+  float wv[TAPS][8], bv[8], win[TAPS - 1][8];
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) load8(w + (size_t)j * C + c, wv[j]);
+  if (bias) load8(bias + c, bv);
+  else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) bv[k] = 0.f;
+  }
+  // the thread's rows and their sequences are requested together, before any arithmetic (rows behind the last token
+  // repeat it and are not stored)
+  float cur[CONV_TOKS][8];
+  int seq[CONV_TOKS];
+#pragma unroll
+  for (int i = 0; i < CONV_TOKS; ++i) {
+    const int t = min(t0 + i, n - 1);
+    seq[i] = seq_of_token[t];
+    load8(u + (size_t)t * u_stride + col0 + c, cur[i]);
+  }
+  int prev = -1;
+#pragma unroll
+  for (int i = 0; i < CONV_TOKS; ++i) {
+    const int t = t0 + i;
+    if (t >= n) break;
+    const int s = seq[i];
+    if (s != prev) {  // the first token of this thread, or of a sequence: the window comes from memory
+      const int first = q_start[s];
+      const int r0 = t - first;
+      const T* carried = state + (size_t)state_slot[s] * (TAPS - 1) * C;
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) {
+        const int r = r0 - (TAPS - 1) + j;
+        if (r >= 0) load8(u + (size_t)(first + r) * u_stride + col0 + c, win[j]);
+        else load8(carried + (size_t)(TAPS - 1 + r) * C + c, win[j]);
+      }
+      prev = s;
+    }
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float a = bv[k];
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) a = fmaf(wv[j][k], win[j][k], a);
+      acc[k] = silu_out<T>(fmaf(wv[TAPS - 1][k], cur[i][k], a));
+    }
+    store8(out + (size_t)t * C + c, acc);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int j = 0; j + 1 < TAPS - 1; ++j) win[j][k] = win[j + 1][k];
+      win[TAPS - 2][k] = cur[i][k];
+    }
+  }
+}
+
 // After the convolution: each sequence's carried inputs become its last taps - 1 inputs (older carried
 // inputs move up when the step brought fewer).  In place: slot i is written from slot i + q_len or from u.
 template <typename T>
@@ -454,6 +522,23 @@ DLI_EXPORT int dli_causal_conv_silu(void* out, const void* u, long long u_stride
   cudaError_t e;
   if ((C % 8) == 0 && (col0 % 8) == 0 && (u_stride % 8) == 0 && (((uintptr_t)out | (uintptr_t)u | (uintptr_t)state | (uintptr_t)bias | (uintptr_t)w) & 15) == 0) {
     const int items = C / 8;
+    if (taps >= 2 && taps <= 4 && n > 64) {  // portions: a sliding window in registers
+      const int wt = items >= 128 ? 128 : 64;
+      const dim3 wgrid((n + CONV_TOKS - 1) / CONV_TOKS, (items + wt - 1) / wt);
+#define DLI_CONV_WIN(T, TAPS)                                                                                                      \
+  return (int)launch_pdl((causal_conv_silu_window_kernel<T, TAPS>), wgrid, dim3(wt), 0, stream, 1, (T*)out, (const T*)u, u_stride, col0, w, \
+                         bias, (const T*)state, seq_of_token, q_start, state_slot, n, C)
+      if (dtype == DLI_F32) {
+        if (taps == 2) DLI_CONV_WIN(float, 2);
+        if (taps == 3) DLI_CONV_WIN(float, 3);
+        DLI_CONV_WIN(float, 4);
+      } else {
+        if (taps == 2) DLI_CONV_WIN(__nv_bfloat16, 2);
+        if (taps == 3) DLI_CONV_WIN(__nv_bfloat16, 3);
+        DLI_CONV_WIN(__nv_bfloat16, 4);
+      }
+#undef DLI_CONV_WIN
+    }
     const dim3 vblock(32, 8), vgrid((n + 7) / 8, (items + 31) / 32);
     if (dtype == DLI_F32)
       e = launch_pdl((causal_conv_silu_vec_kernel<float>), vgrid, vblock, 0, stream, 1, (float*)out, (const float*)u, u_stride, col0, w, bias,

@@ -157,7 +157,7 @@ def case_every_configuration_whole_prompt_and_layers(tmp_path, device, dtype):
     """Whole prompts in every configuration: logits, and the stream after every layer run (in float32)."""
     for name, cfg in CONFIGS.items():
         w = make_model(tmp_path / name, cfg, seed=3)
-        toks = tokens_for(cfg, 29, seed=1)
+        toks = tokens_for(cfg, 77, seed=1)  # more than the 64 tokens from which portions take their own convolution kernel
         want, layers = plain.forward(cfg, w, toks, return_layers=True)
         s = Session(tmp_path / name, device, dtype)
         s.model.trace_layers = []

@@ -117,9 +117,9 @@ def _batch(q_lens):
 @pytest.mark.parametrize("dtype,tol", DTYPES)
 @pytest.mark.parametrize("taps", [1, 2, 4])
 @pytest.mark.parametrize("C,col0", [(150, 11), (152, 8), (2304, 16)])
-def test_causal_conv_and_its_state(dtype, tol, taps, C, col0):
+@pytest.mark.parametrize("q_lens", [[1, 5, 2, 1], [1, 70, 2, 13]], ids=["few_tokens", "portions"])  # portions take the kernel with a window in registers
+def test_causal_conv_and_its_state(dtype, tol, taps, C, col0, q_lens):
     slots = 6
-    q_lens = [1, 5, 2, 1]
     q_start, seq_of = _batch(q_lens)
     n = int(q_start[-1])
     slot = torch.tensor([4, 0, 5, 2], dtype=torch.int32)
