@@ -132,6 +132,7 @@ struct Epilogue {
   float* h;
   const float* gain;
   float* out_ssq;
+  int act;  // EP_STORE: an activation applied to the (bfloat16-rounded) sums before they are stored: 0 none, 1 relu^2, 2 gelu-tanh, 3 silu
   const float* in_ssq;
   int in_tiles;
   float in_eps, in_inv_size;
@@ -188,6 +189,19 @@ __device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, co
   const int kvh = head - ep.nh;
   if (kvh < ep.nkv) ep.k_pool[(((size_t)page * ep.nkv + kvh) * ep.page_size + off) * ep.d + i] = b;
   else ep.v_pool[(((size_t)page * ep.nkv + (kvh - ep.nkv)) * ep.page_size + off) * ep.d + i] = b;
+}
+
+// The activation of a plain feed-forward on a sum rounded to bfloat16 first, as the library's product would have stored it:
+// a token's activations then do not depend on whether its step took this kernel or the library and the activation kernel.
+__device__ __forceinline__ float store_activation(int act, float v) {
+  if (act == 0) return v;
+  const float z = __bfloat162float(__float2bfloat16_rn(v));
+  if (act == 1) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  if (act == 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.f + expf(-z));
 }
 
 // (relaxed: the barrier only tells that every CTA of the cluster runs and has set up its mbarriers, which
@@ -389,7 +403,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
       } else if (fused) {
         recv[t * BM + fl] = __uint_as_float(r[j]) * (scaled ? rstd[t] : 1.f);
       } else if (f < features) {
-        store_out(out, out_f32, (size_t)t * features + f, __uint_as_float(r[j]) * (scaled ? rstd[t] : 1.f));
+        store_out(out, out_f32, (size_t)t * features + f, store_activation(ep.act, __uint_as_float(r[j]) * (scaled ? rstd[t] : 1.f)));
       }
     }
   }
@@ -406,7 +420,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
       for (int s2 = 0; s2 < slices; ++s2) acc += recv[(s2 * owned_max + ti) * BM + fl];  // slice 0 first
       if (scaled) acc *= rstd[t];
       if (fused) fin[ti * BM + fl] = acc;
-      else if (f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
+      else if (f < features) store_out(out, out_f32, (size_t)t * features + f, store_activation(ep.act, acc));
     }
   }
   if (fused) {
@@ -535,6 +549,18 @@ DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void
   ep.mode = EP_STORE;
   if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
   return launch_skinny(out, out_f32, x, w, tokens, features, K, slices, max_stages, ep, stream);
+}
+
+// out[tokens, features] = act(x W^T) in bfloat16: the up product of a plain feed-forward with its activation
+// (1 relu^2, 2 gelu-tanh, 3 silu) in the epilogue.
+DLI_EXPORT int dli_skinny_gemm_act(void* out, const void* x, const void* w, int tokens, int features, int K, int slices, int act,
+                                   const float* in_ssq, int in_tiles, float in_eps, int in_size, cudaStream_t stream) {
+  if (act < 1 || act > 3) return DLI_ERR_UNSUPPORTED;
+  Epilogue ep = {};
+  ep.mode = EP_STORE;
+  ep.act = act;
+  if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
+  return launch_skinny(out, 0, x, w, tokens, features, K, slices, 0, ep, stream);
 }
 
 // act[tokens, features / 2] = silu(gate) * up, for weights whose rows are interleaved in blocks of 64

@@ -662,6 +662,23 @@ def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor) -> torch.Ten
     return out
 
 
+def skinny_gemm_act(x, weight: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(x W^T) in one kernel: the decode matrix product with the activation of a plain feed-forward (``relu2``,
+    ``gelu_tanh``, ``silu``) in its epilogue, applied to the sums rounded to bfloat16 (what the product alone would have
+    stored).  Returns bfloat16 [tokens, features]."""
+    x, scale = _row_scale(x, "skinny_gemm_act")
+    _need(x, "x", torch.bfloat16), _need(weight, "weight", torch.bfloat16)
+    tokens, K = x.shape
+    features = weight.shape[0]
+    if weight.shape[1] != K or not skinny_gemm_supported(tokens, K) or kind not in ACTIVATIONS:
+        raise KernelError("skinny_gemm_act: sizes or activation not supported")
+    out = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_act", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int] + _ROW_SCALE_ARGS + [c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight), tokens, features, K, skinny_gemm_slices(tokens, features, K), ACTIVATIONS[kind] + 1, *scale, _stream()),
+           "skinny_gemm_act")
+    return out
+
+
 def skinny_rotary_supported(head_dim: int) -> bool:
     return head_dim >= 2 and 128 % head_dim == 0
 

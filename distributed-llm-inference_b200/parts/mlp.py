@@ -87,4 +87,6 @@ class DenseActMLP(Part):
         self.w_up, self.w_down = tensors[self.names["up"]], tensors[self.names["down"]]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if fused_epilogue(x):  # a decode step's few tokens: the activation rides in the up product's epilogue
+            return project(ops.skinny_gemm_act(x, self.w_up, self.activation), self.w_down)
         return project(ops.activation(project(x, self.w_up), self.activation), self.w_down)

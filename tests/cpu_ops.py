@@ -294,6 +294,10 @@ def skinny_gemm_swiglu(x, weight_tiled):
     return out
 
 
+def skinny_gemm_act(x, weight, kind):
+    return activation(_sums(x, weight).to(torch.bfloat16), kind)
+
+
 def skinny_gemm_rotary(x, wqkv, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim, rotary_dim, page_size, write_kv):
     qkv = _sums(x, wqkv)  # rotated in float32, rounded once (as the kernel's epilogue does)
     pools = (torch.empty_like(k_pool, dtype=torch.float32), torch.empty_like(v_pool, dtype=torch.float32)) if write_kv else (None, None)
@@ -381,7 +385,7 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "rotary_table": rotary_table, "rotary_store": rotary_store, "silu_mul": silu_mul, "paged_attention_simt": paged_attention_simt,
        "paged_attention_mma": paged_attention_mma, "paged_decode_tma": paged_decode_tma, "paged_prefill_tc": paged_prefill_tc,
        "skinny_gemm_slices": skinny_gemm_slices, "skinny_gemm": skinny_gemm, "skinny_gemm_residual": skinny_gemm_residual,
-       "skinny_gemm_swiglu": skinny_gemm_swiglu, "skinny_gemm_rotary": skinny_gemm_rotary, "dense_gemm": dense_gemm,
+       "skinny_gemm_swiglu": skinny_gemm_swiglu, "skinny_gemm_act": skinny_gemm_act, "skinny_gemm_rotary": skinny_gemm_rotary, "dense_gemm": dense_gemm,
        "dense_gemm_swiglu": dense_gemm_swiglu, "dense_gemm_rotary": dense_gemm_rotary,
        "sample": sample, "post_add_layernorm": post_add_layernorm, "stream_reinject": stream_reinject, "activation": activation,
        "qk_norm_rotary_store": qk_norm_rotary_store, "sigmoid_gate": sigmoid_gate, "causal_conv_silu": causal_conv_silu,

@@ -246,3 +246,17 @@ def test_sink_in_the_bfloat16_attention_kernels(d, page, sink):
                                     150, singles, nh, scale, None, sink=sink)
             _close(got, want, 3e-2, f"splits {splits}")
     assert ops.device_wait_errors() == {}
+
+
+@pytest.mark.parametrize("kind", ["relu2", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("tokens,K,features", [(1, 256, 384), (5, 2048, 8192), (8, 96, 200)])
+def test_decode_product_with_the_activation_in_its_epilogue(kind, tokens, K, features):
+    """Equal to the plain product (rounded to bfloat16) followed by the activation kernel, bit for bit up to the
+    product's own summation order."""
+    x = (_rand(tokens, K, seed=1)).to(torch.bfloat16)
+    w = (_rand(features, K, seed=2) / K**0.5).to(torch.bfloat16)
+    want = ref.skinny_gemm_act(x, w, kind)
+    got = ops.skinny_gemm_act(x.cuda(), w.cuda(), kind)
+    _close(got, want, 2e-2, kind)
+    two_steps = ops.activation(ops.skinny_gemm(x.cuda(), w.cuda()), kind)
+    assert (got.float() - two_steps.float()).abs().max().item() <= 2e-2 * max(1.0, want.float().abs().max().item())
