@@ -50,3 +50,31 @@ def test_trace_replay_with_four_state_slots(dtype, tmp_path):
             step += 1
     finally:
         run.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_small_mixed_steps_replayed_from_graphs(dtype, tmp_path):
+    """A step shape that keeps coming (a short portion of one request beside single tokens of two others) is captured as
+    a CUDA graph after 32 sightings; its padding rows use the scratch page and the scratch state slot.  Logits before
+    and after the capture equal the plain model's."""
+    cfg = suite.CONFIGS["mixed_loop"]
+    w = suite.make_model(tmp_path / "m", cfg, seed=43)
+    s = suite.Session(tmp_path / "m", "cuda:0", dtype, pages=120, page_size=8)
+    assert s.runner.graphs is not None
+    long = suite.tokens_for(cfg, 3 * 48 + 1, seed=90)
+    b, c = suite.tokens_for(cfg, 60, seed=91), suite.tokens_for(cfg, 60, seed=92)
+    want = {"a": plain.forward(cfg, w, long), "b": plain.forward(cfg, w, b), "c": plain.forward(cfg, w, c)}
+    s.step(("b", b[:10], []), ("c", c[:9], []))
+    got = {"a": [], "b": [], "c": []}
+    at = {"a": 0, "b": 10, "c": 9}
+    for _ in range(48):
+        out = s.step(("a", long[at["a"] : at["a"] + 3], [0, 1, 2]), ("b", [b[at["b"]]], [0]), ("c", [c[at["c"]]], [0]))
+        got["a"].append(out[0:3]), got["b"].append(out[3:4]), got["c"].append(out[4:5])
+        at["a"] += 3
+        at["b"] += 1
+        at["c"] += 1
+    assert s.runner.mixed_graph_steps >= 10, s.runner.graphs.mixed_failure
+    for r, first in (("a", 0), ("b", 10), ("c", 9)):
+        seq = {"a": long, "b": b, "c": c}[r]
+        suite.close(np.concatenate(got[r]), want[r][first : at[r]], dtype, f"request {r}",
+                    suite.rounding_error(tmp_path / "m", "cuda:0", dtype, seq, want[r]))
