@@ -323,6 +323,40 @@ def case_window(tmp_path, device, dtype):
     close(np.concatenate(got), want, dtype, "window")
 
 
+def case_one_key_at_the_window_s_edge(tmp_path, device, dtype):
+    """The far-key construction with a window of 24 keys: the deciding key sits on the last place the window still
+    holds (it decides), and one place further back (it must not be seen); in a prompt and decoded alone, with the
+    window's edge inside a page and on a page border."""
+    window = 24
+    cfg = config([attention(heads=2, kv_heads=1, dim=16, rot_dims=0, factor=None, scale=3.0, window=window)], width=32, vocab=50, no_mlp=(0,))
+    eps = cfg["norm"]["eps"]
+    w = make_model(tmp_path / "edge", cfg, seed=19)
+    h = plain.layer_norm(w["embed"], w["l0.norm1"], eps)
+    q = (plain.rms_unit(h @ w["l0.mix.q"].T, eps) * w["l0.mix.q.norm"])[:, :16]
+    k = plain.rms_unit(h @ w["l0.mix.k"].T, eps) * w["l0.mix.k.norm"]
+    scores = (q @ k.T) * cfg["layers"][0]["mixer"]["scale"]
+    asker = next(t for t in range(50) if scores[t].argmax() != t and np.sort(scores[t])[-1] - np.sort(scores[t])[-2] > 8)
+    key = int(scores[asker].argmax())
+    noise = [t for t in range(50) if scores[asker, t] < scores[asker, key] - 8 and t != asker]
+    s = Session(tmp_path / "edge", device, dtype, pages=24, page_size=8)
+    for length in (60, 57):  # the oldest visible key at 36 (inside a page) and at 33; its neighbour outside at 35 and 32 (a page's first key)
+        last = length - 1
+        inside, outside = last - window + 1, last - window
+        logits = {}
+        for name, place in (("inside", inside), ("outside", outside)):
+            toks = [noise[i] for i in np.random.default_rng(length).integers(0, len(noise), length)]
+            toks[place] = key
+            toks[last] = asker
+            want = plain.forward(cfg, w, toks)
+            logits[name] = want[-1]
+            close(s.whole("p", toks)[-1], want[-1], dtype, f"key {name} the window, prompt of {length}")
+            s.free("p")
+            s.step(("d", toks[:-1], []))
+            close(s.step(("d", toks[-1:], [0]))[0], want[-1], dtype, f"key {name} the window, decoded at {last}")
+            s.free("d")
+        assert np.abs(logits["inside"] - logits["outside"]).max() > 0.2, "the key at the window's edge does not matter enough for this test"
+
+
 def case_greedy_generation_through_the_engine(tmp_path, device, dtype):
     """LLMEngine.generate (scheduler, batching, sampler) against greedy decoding with the plain model."""
     from dli_b200 import LLMEngine, SamplingParams, SchedulerConfig
