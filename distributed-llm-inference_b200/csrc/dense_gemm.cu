@@ -109,6 +109,7 @@ struct DenseParams {
   __nv_bfloat16* k_pool;
   __nv_bfloat16* v_pool;
   int nh, nkv, d, rot, page_size, write_kv;
+  int act;        // EP_STORE: an activation on the (bfloat16-rounded) sums before they are stored: 0 none, 1 relu^2, 2 gelu-tanh, 3 silu
   int skip_tile;  // -1 in every launch of the engine: the k step whose copies a test leaves out (dli_dense_gemm_wait_test)
 };
 
@@ -154,8 +155,18 @@ __device__ __forceinline__ void epilogue_row(const DenseParams& p, uint32_t acc,
 #pragma unroll 1
     for (int c = 0; c < BN && f0 + c < p.features; c += 32) {
       float f[32];
-      load_chunk(acc + c, f);
+      load_chunk(acc + c, f, p.act != 0);
       if (live) {
+        if (p.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { const float r = fmaxf(f[j], 0.f); f[j] = r * r; }
+        } else if (p.act == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = 0.5f * f[j] * (1.f + tanhf(0.7978845608028654f * (f[j] + 0.044715f * f[j] * f[j] * f[j])));
+        } else if (p.act == 3) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = f[j] / (1.f + expf(-f[j]));
+        }
 #pragma unroll
         for (int j = 0; j < 32; j += 8)
           if (f0 + c + j < p.features) store8(dst + c + j, f + j);  // features are a multiple of 8
@@ -489,6 +500,17 @@ DLI_EXPORT int dli_dense_gemm(void* out, const void* x, const void* w, int token
   DenseParams p = {};
   p.out = (__nv_bfloat16*)out;
   p.mode = EP_STORE;
+  return launch_dense(p, x, w, tokens, features, K, stream);
+}
+
+// out [tokens, features] = act(x w^T): the up product of a plain feed-forward with its activation (1 relu^2, 2 gelu-tanh,
+// 3 silu) in the epilogue.
+DLI_EXPORT int dli_dense_gemm_act(void* out, const void* x, const void* w, int tokens, int features, int K, int act, cudaStream_t stream) {
+  if (act < 1 || act > 3) return DLI_ERR_UNSUPPORTED;
+  DenseParams p = {};
+  p.out = (__nv_bfloat16*)out;
+  p.mode = EP_STORE;
+  p.act = act;
   return launch_dense(p, x, w, tokens, features, K, stream);
 }
 

@@ -64,12 +64,12 @@ def _dense_candidate(x, features: int) -> bool:
 
 
 def dense_product(x, features: int, epilogue: str) -> bool:
-    """Whether the product of these activations with a [features, K] weight, followed by ``epilogue`` ("swiglu" or
-    "rotary"), goes to the engine's product for many tokens."""
+    """Whether the product of these activations with a [features, K] weight, followed by ``epilogue`` ("swiglu", "act": a
+    plain feed-forward's activation, or "rotary"), goes to the engine's product for many tokens."""
     if not _dense_candidate(x, features):
         return False
     tiles, pairs = _dense_tiles(x.shape[0], features), max(1, sm_count() // 2)
-    if epilogue == "swiglu":
+    if epilogue in ("swiglu", "act"):  # the activation of a feed-forward rides for nothing under the next tile's products
         return True
     if epilogue == "rotary":
         return tiles <= pairs or tiles / (-(-tiles // pairs) * pairs) >= WAVE_FILL_MIN

@@ -750,6 +750,18 @@ def dense_gemm(x, weight: torch.Tensor, out: torch.Tensor | None = None) -> torc
     return out
 
 
+def dense_gemm_act(x, weight: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(x W^T) in the product's epilogue (``relu2``, ``gelu_tanh``, ``silu``), applied to the sums rounded to bfloat16.
+    Returns bfloat16 [tokens, features]."""
+    tokens, features, K = _dense_sizes(x, weight, "dense_gemm_act")
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"dense_gemm_act: activation {kind!r} not supported")
+    out = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
+    f = _fn("dense_gemm.cu", "dli_dense_gemm_act", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight), tokens, features, K, ACTIVATIONS[kind] + 1, _stream()), "dense_gemm_act")
+    return out
+
+
 def dense_gemm_swiglu(x, weight_tiled: torch.Tensor) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) in the product's epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate
     rows, then the 64 up rows of the same features.  Returns bfloat16 [tokens, I]."""

@@ -89,4 +89,6 @@ class DenseActMLP(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if fused_epilogue(x):  # a decode step's few tokens: the activation rides in the up product's epilogue
             return project(ops.skinny_gemm_act(x, self.w_up, self.activation), self.w_down)
+        if dense_product(x, self.inter, "act"):  # a long portion: the same in the epilogue of the product for many tokens
+            return project(ops.dense_gemm_act(x, self.w_up, self.activation), self.w_down)
         return project(ops.activation(project(x, self.w_up), self.activation), self.w_down)

@@ -316,6 +316,10 @@ def dense_gemm(x, weight, out=None):
     return skinny_gemm(x, weight, torch.bfloat16, out=out)
 
 
+def dense_gemm_act(x, weight, kind):
+    return skinny_gemm_act(x, weight, kind)
+
+
 def dense_gemm_swiglu(x, weight_tiled):
     return skinny_gemm_swiglu(x, weight_tiled)
 
@@ -386,7 +390,7 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "paged_attention_mma": paged_attention_mma, "paged_decode_tma": paged_decode_tma, "paged_prefill_tc": paged_prefill_tc,
        "skinny_gemm_slices": skinny_gemm_slices, "skinny_gemm": skinny_gemm, "skinny_gemm_residual": skinny_gemm_residual,
        "skinny_gemm_swiglu": skinny_gemm_swiglu, "skinny_gemm_act": skinny_gemm_act, "skinny_gemm_rotary": skinny_gemm_rotary, "dense_gemm": dense_gemm,
-       "dense_gemm_swiglu": dense_gemm_swiglu, "dense_gemm_rotary": dense_gemm_rotary,
+       "dense_gemm_swiglu": dense_gemm_swiglu, "dense_gemm_act": dense_gemm_act, "dense_gemm_rotary": dense_gemm_rotary,
        "sample": sample, "post_add_layernorm": post_add_layernorm, "stream_reinject": stream_reinject, "activation": activation,
        "qk_norm_rotary_store": qk_norm_rotary_store, "sigmoid_gate": sigmoid_gate, "causal_conv_silu": causal_conv_silu,
        "conv_state_update": conv_state_update, "ssm_scan": ssm_scan, "gated_group_rmsnorm": gated_group_rmsnorm}

@@ -260,3 +260,14 @@ def test_decode_product_with_the_activation_in_its_epilogue(kind, tokens, K, fea
     _close(got, want, 2e-2, kind)
     two_steps = ops.activation(ops.skinny_gemm(x.cuda(), w.cuda()), kind)
     assert (got.float() - two_steps.float()).abs().max().item() <= 2e-2 * max(1.0, want.float().abs().max().item())
+
+
+@pytest.mark.parametrize("kind", ["relu2", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("tokens,K,features", [(700, 256, 384), (1024, 512, 1032)])
+def test_long_portion_product_with_the_activation_in_its_epilogue(kind, tokens, K, features):
+    x = (_rand(tokens, K, seed=1)).to(torch.bfloat16)
+    w = (_rand(features, K, seed=2) / K**0.5).to(torch.bfloat16)
+    want = ref.dense_gemm_act(x, w, kind)
+    got = ops.dense_gemm_act(x.cuda(), w.cuda(), kind)
+    _close(got, want, 2e-2, kind)
+    assert ops.dense_gemm_error() == 0
