@@ -494,7 +494,7 @@ int launch_scan(float* y, const T* xbc, const T* u, long long u_stride, int dt_c
   // would leave an SM with fewer than four warps, as one long prompt on a few heads does.  (Measured on a B200, 4,096
   // tokens, state 128 x 64: 64 heads 1.70 ms with 8 and 1.42 with 16; 128 heads 1.74 and 2.46; 32 made everything slower.)
   const long long pairs = (long long)heads * num_seqs * ((P + 1) / 2);
-  const int ns = (pairs * 8 < 4LL * 32 * sm_count() && N > 32) ? 16 : 8;
+  const int ns = ((pairs * 8 < 4LL * 32 * sm_count() && N > 32) || N > 256) ? 16 : 8;  // (a state above 256 takes 16 threads a pair to hold it)
   const int quads = (N + 4 * ns - 1) / (4 * ns);  // float4 runs of n per thread
 #define DLI_SCAN(NPT, NS) \
   return launch_scan_shape<T, NPT, NS>(y, xbc, u, u_stride, dt_col, dt_bias, A_log, D, state, q_start, state_slot, num_seqs, heads, P, N, groups, max_len, stream)
@@ -507,6 +507,7 @@ int launch_scan(float* y, const T* xbc, const T* u, long long u_stride, int dt_c
     if (quads <= 1) DLI_SCAN(4, 16);
     if (quads <= 2) DLI_SCAN(8, 16);
     if (quads <= 4) DLI_SCAN(16, 16);
+    if (quads <= 8) DLI_SCAN(32, 16);
   }
 #undef DLI_SCAN
   return DLI_ERR_UNSUPPORTED;

@@ -981,7 +981,7 @@ def conv_state_update(state: torch.Tensor, u: torch.Tensor, col0: int, q_start: 
            "conv_state_update")
 
 
-SSM_SCAN_MAX_STATE = 256
+SSM_SCAN_MAX_STATE = 512
 
 
 def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
@@ -999,7 +999,7 @@ def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, d
     if (xbc.shape[1] != heads * P + 2 * groups * N or tuple(y.shape) != (n, heads * P) or u.shape[0] != n or dt_col + heads > u.shape[1]
             or heads % groups or N > SSM_SCAN_MAX_STATE or dt_bias.numel() != heads or a_log.numel() != heads or d_skip.numel() != heads
             or q_start.numel() != state_slot.numel() + 1):
-        raise KernelError("ssm_scan: shapes do not agree (or the state size is above 256)")
+        raise KernelError(f"ssm_scan: shapes do not agree (or the state size is above {SSM_SCAN_MAX_STATE})")
     f = _fn("ssm.cu", "dli_ssm_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
             + [c_int] * 7 + [c_void_p])
     _check(f(_ptr(y), _ptr(xbc), _ptr(u), u.stride(0), dt_col, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(q_start),

@@ -138,7 +138,7 @@ def test_causal_conv_and_its_state(dtype, tol, taps, C, col0, q_lens):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("heads,P,N,groups", [(6, 48, 32, 2), (4, 64, 128, 1), (3, 20, 10, 3), (2, 96, 256, 2), (8, 8, 64, 4), (1, 5, 33, 1), (160, 40, 24, 8)])
+@pytest.mark.parametrize("heads,P,N,groups", [(6, 48, 32, 2), (4, 64, 128, 1), (3, 20, 10, 3), (2, 96, 256, 2), (8, 8, 64, 4), (1, 5, 33, 1), (160, 40, 24, 8), (2, 16, 320, 1), (1, 8, 512, 1)])
 def test_ssm_scan(dtype, tol, heads, P, N, groups):
     q_lens = [1, 77, 2, 32]
     q_start, _ = _batch(q_lens)
