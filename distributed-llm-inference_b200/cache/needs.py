@@ -19,6 +19,8 @@ class PagedKVNeed:
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    # the values are read from the keys' rows (their leading numbers): no value pool is kept, ``LayerCache.v`` is ``k``
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

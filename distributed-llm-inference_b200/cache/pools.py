@@ -69,7 +69,7 @@ class CachePools:
         for need, pages, own in zip(self.group_needs, pages_per_group, owners):
             shape = (len(own), pages + 1, need.num_kv_heads, page_size, need.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(self.k[-1] if need.values_in_keys else torch.zeros(shape, dtype=dtype, device=device))
         self.scratch_state_slot = max_requests
         self.layer_caches: list[LayerCache] = []
         for i, answer in enumerate(needs):
@@ -108,5 +108,5 @@ class CachePools:
         for i, answer in enumerate(needs):
             need = paged_need_of(answer)
             if need is not None and run_order[i].cache_of is None:
-                out[group_of_step[i]] += 2 * need.num_kv_heads * page_size * need.head_dim * dtype.itemsize
+                out[group_of_step[i]] += (1 if need.values_in_keys else 2) * need.num_kv_heads * page_size * need.head_dim * dtype.itemsize
         return out

@@ -13,7 +13,7 @@ from dataclasses import dataclass
 from typing import Any
 
 from .llama import UnsupportedModelError
-from .spec import LayerSpec, ModelSpec, PartSpec, RunStep
+from .spec import LayerSpec, ModelSpec, PartSpec, RunStep, looped_run_order
 
 
 def _keys(d: dict, where: str, required: tuple[str, ...], optional: tuple[str, ...] = ()) -> None:
@@ -159,13 +159,8 @@ def _parse_mamba2(m: dict, where: str) -> Mamba2MixerConfig:
 def pazenex_run_order(cfg: PazenexConfig) -> tuple[RunStep, ...]:
     """Layers before the looped span once, the span ``times`` times in a row (each pass a run step of its own per
     layer, hence a cache of its own), the rest once.  The first layer of pass t is entered through entry t."""
-    n = len(cfg.layers)
-    if cfg.loop is None:
-        return tuple(RunStep(i) for i in range(n))
-    steps = [RunStep(i) for i in range(cfg.loop.start)]
-    for t in range(cfg.loop.times):
-        steps += [RunStep(i, entry=t if i == cfg.loop.start else None) for i in range(cfg.loop.start, cfg.loop.stop)]
-    return tuple(steps + [RunStep(i) for i in range(cfg.loop.stop, n)])
+    loop = cfg.loop
+    return looped_run_order(len(cfg.layers), None if loop is None else (loop.start, loop.stop, loop.times))
 
 
 def pazenex_model_spec(cfg: PazenexConfig) -> ModelSpec:

@@ -15,6 +15,7 @@ from typing import Any, Callable
 from .llama import LlamaConfig, UnsupportedModelError, llama_model_spec
 from .pazenex import PazenexConfig, pazenex_model_spec
 from .spec import ModelSpec
+from .sugonex import SugonexConfig, sugonex_model_spec
 
 
 @dataclass(frozen=True)
@@ -60,3 +61,4 @@ register_architecture(
     Architecture("LlamaForCausalLM", LlamaConfig.from_hf_dict, llama_model_spec, model_types=("llama",))
 )
 register_architecture(Architecture("Pazenex", PazenexConfig.from_dict, pazenex_model_spec))
+register_architecture(Architecture("Sugonex", SugonexConfig.from_dict, sugonex_model_spec))

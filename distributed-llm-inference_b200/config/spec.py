@@ -68,3 +68,17 @@ class ModelSpec:
                     raise ValueError(f"run_order[{i}].cache_of must name an earlier entry")
                 if self.run_order[step.cache_of].cache_of is not None:
                     raise ValueError(f"run_order[{i}].cache_of names an entry that owns no cache")
+
+
+def looped_run_order(num_layers: int, loop: tuple[int, int, int] | None) -> tuple[RunStep, ...]:
+    """Run order of a model whose layers ``start .. stop - 1`` run ``times`` times in a row with the same weights
+    (``loop`` = (start, stop, times), or None): the layers before the span once, the span pass after pass (each pass a
+    run step of its own per layer, hence a cache of its own), the rest once.  The first layer of pass t is entered
+    through entry t."""
+    if loop is None:
+        return tuple(RunStep(i) for i in range(num_layers))
+    start, stop, times = loop
+    steps = [RunStep(i) for i in range(start)]
+    for t in range(times):
+        steps += [RunStep(i, entry=t if i == start else None) for i in range(start, stop)]
+    return tuple(steps + [RunStep(i) for i in range(stop, num_layers)])

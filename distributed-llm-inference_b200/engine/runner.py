@@ -110,7 +110,8 @@ class ModelRunner:
         layer of their groups, before the step that writes the appended tokens."""
         for c in copies:
             ops.copy_page(self.pools.k[c.group], c.src, c.dst)
-            ops.copy_page(self.pools.v[c.group], c.src, c.dst)
+            if self.pools.v[c.group] is not self.pools.k[c.group]:  # (a group whose values lie in its keys' rows has one pool)
+                ops.copy_page(self.pools.v[c.group], c.src, c.dst)
 
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry], borrow: bool = False, token_source: torch.Tensor | None = None) -> torch.Tensor:

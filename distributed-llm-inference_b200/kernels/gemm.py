@@ -82,6 +82,8 @@ def project(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_t
     the decode kernel serves, which applies the factor."""
     if isinstance(x, ops.ScaledRows) or decode_product(x, max_tokens):
         return ops.skinny_gemm(x, weight, out_dtype or x.dtype)
+    if out_dtype == torch.float32 and x.dtype != torch.float32:
+        return logits_product(x, weight)
     y = linear(x, weight)
     return y if out_dtype in (None, y.dtype) else y.to(out_dtype)
 
@@ -104,3 +106,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
     if torch.backends.cuda.matmul.allow_tf32:
         raise RuntimeError("linear: TF32 was switched on; the float32 path must stay true 32-bit")
     return torch.matmul(x, weight.t(), out=out)
+
+
+def _need_device(x: torch.Tensor, what: str) -> None:
+    if not x.is_cuda:
+        raise RuntimeError(f"{what}: the engine has no CPU path")
+
+
+def heads_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, a, :] = x[t, a, :] @ weight[a]: one product per head a, batched (x [n, heads, in] and out [n, heads, features]
+    may be column slices of wider rows; weight [heads, in, features] any strides).  The library's strided-batched
+    product, float32 accumulation."""
+    _need_device(x, "heads_product")
+    if torch.backends.cuda.matmul.allow_tf32:
+        raise RuntimeError("heads_product: TF32 was switched on; the float32 path must stay true 32-bit")
+    return torch.bmm(x.transpose(0, 1), weight, out=out.transpose(0, 1))
+
+
+def logits_product(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """x [n, in] (bfloat16 or float32) times weight [out, in] transposed, the float32 sums returned as they are."""
+    _need_device(x, "logits_product")
+    if x.dtype == torch.float32:
+        return linear(x, weight)
+    return torch.mm(x, weight.t(), out_dtype=torch.float32)

@@ -216,18 +216,64 @@ def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tenso
     return table
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, tiled: bool = False) -> None:
-    """out[n, I] = silu(gate) * up.  gate_up [n, 2 I] holds gate | up side by side, or, ``tiled``
-    (I a multiple of 64), blocks of 128 columns: 64 gate features, then the same 64 up features."""
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # what a gated feed-forward may apply to its gate
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, tiled: bool = False, activation: str = "silu") -> None:
+    """out[n, I] = act(gate) * up, act = silu or another of GLU_ACTIVATIONS.  gate_up [n, 2 I] holds gate | up side by
+    side, or, ``tiled`` (I a multiple of 64), blocks of 128 columns: 64 gate features, then the same 64 up features."""
     _need(out, "out"), _need(gate_up, "gate_up", out.dtype)
     n, I = out.shape
-    if out.dtype not in DT_CODE or tuple(gate_up.shape) != (n, 2 * I) or (tiled and I % 64):
-        raise KernelError("silu_mul: shapes or dtype do not agree")
-    f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), _ptr(gate_up), n, I, int(tiled), DT_CODE[out.dtype], _stream()), "silu_mul")
+    if out.dtype not in DT_CODE or tuple(gate_up.shape) != (n, 2 * I) or (tiled and I % 64) or activation not in GLU_ACTIVATIONS:
+        raise KernelError("silu_mul: shapes, dtype or activation do not agree")
+    f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(gate_up), n, I, int(tiled), GLU_ACTIVATIONS[activation], DT_CODE[out.dtype], _stream()), "silu_mul")
+
+
+def add_rmsnorm_pair(y1: torch.Tensor, y2: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor | None, b: torch.Tensor | None,
+                     w1: torch.Tensor, w2: torch.Tensor | None, eps: float, rows: torch.Tensor | None = None) -> None:
+    """v = h[s] + (a[s] + b[s]) (either may be None), y1[r] = v / rms(v) * w1 and, if ``y2``, y2[r] = v / rms(v) * w2,
+    with s = rows[r] (or r): two norms of one stream that differ in their weights only share the sum of squares.
+    Without ``rows`` v is written back to ``h``.  All arithmetic float32."""
+    _need(y1, "y1"), _need(h, "h", torch.float32), _need(w1, "w1", torch.float32)
+    H = h.shape[1]
+    n_rows = y1.shape[0]
+    if y1.dtype not in DT_CODE or y1.shape[1] != H or w1.numel() != H:
+        raise KernelError("add_rmsnorm_pair: shapes or dtype do not agree")
+    if (y2 is None) != (w2 is None):
+        raise KernelError("add_rmsnorm_pair: a second output needs a second weight")
+    if y2 is not None:
+        _need(y2, "y2", y1.dtype), _need(w2, "w2", torch.float32)
+        if y2.shape != y1.shape or w2.numel() != H:
+            raise KernelError("add_rmsnorm_pair: y2 and w2 must match y1 and w1")
+    for d, name in ((a, "a"), (b, "b")):
+        if d is not None:
+            _need(d, name, y1.dtype)
+            if d.shape != h.shape:
+                raise KernelError(f"add_rmsnorm_pair: {name} and h differ in shape")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() != n_rows:
+            raise KernelError("add_rmsnorm_pair: one output row per entry of rows")
+    elif n_rows != h.shape[0]:
+        raise KernelError("add_rmsnorm_pair: y1 and h differ in rows")
+    f = _fn("elementwise.cu", "dli_add_rmsnorm_pair",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(y1), _ptr(y2), _ptr(h), _ptr(a), _ptr(b), _ptr(w1), _ptr(w2), _ptr(rows), n_rows, H, eps, DT_CODE[y1.dtype], _stream()),
+           "add_rmsnorm_pair")
+
+
+def scale_softcap(logits: torch.Tensor, scale: float, cap: float) -> None:
+    """logits <- logits * scale, then, if cap > 0, cap * tanh(logits / cap); float32, in place."""
+    _need(logits, "logits", torch.float32)
+    f = _fn("elementwise.cu", "dli_scale_softcap", [c_void_p, c_longlong, c_float, c_float, c_void_p])
+    _check(f(_ptr(logits), logits.numel(), scale, cap, _stream()), "scale_softcap")
 
 
 # ------------------------------------------------------------------ attention
+
+
+SIMT_MAX_HEAD_DIM = 1024
 
 
 def paged_attention_simt(
@@ -255,8 +301,8 @@ def paged_attention_simt(
     _, nkv, page_size, d = k_pool.shape
     if out.dtype not in DT_CODE or out.shape[1] != num_heads * d or qkv.shape[0] != n or qkv.shape[1] < num_heads * d:
         raise KernelError("paged_attention_simt: shapes or dtype do not agree")
-    if d > 256 or num_heads % nkv:
-        raise KernelError(f"paged_attention_simt: head_dim {d} (<= 256) / heads {num_heads} per kv head {nkv} not supported")
+    if d > SIMT_MAX_HEAD_DIM or num_heads % nkv:
+        raise KernelError(f"paged_attention_simt: head_dim {d} (<= {SIMT_MAX_HEAD_DIM}) / heads {num_heads} per kv head {nkv} not supported")
     f = _fn(
         "attention_simt.cu", "dli_paged_attention_simt",
         [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_float, c_int, c_void_p],
@@ -646,19 +692,20 @@ def skinny_gemm_residual(x, weight: torch.Tensor, h: torch.Tensor, gain: torch.T
     return ScaledRows(out, ssq, eps)
 
 
-def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) in one kernel: the decode matrix product with the activation in its
+def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) (act: silu or another of GLU_ACTIVATIONS) in one kernel: the decode matrix product with the activation in its
     epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate rows, then the 64 up rows of
     the same features.  Returns bfloat16 [tokens, I]."""
     x, scale = _row_scale(x, "skinny_gemm_swiglu")
     _need(x, "x", torch.bfloat16), _need(weight_tiled, "weight", torch.bfloat16)
     tokens, K = x.shape
     features = weight_tiled.shape[0]
-    if weight_tiled.shape[1] != K or features % 128 or not skinny_gemm_supported(tokens, K):
-        raise KernelError("skinny_gemm_swiglu: sizes not supported")
+    if weight_tiled.shape[1] != K or features % 128 or not skinny_gemm_supported(tokens, K) or activation not in GLU_ACTIVATIONS:
+        raise KernelError("skinny_gemm_swiglu: sizes or activation not supported")
     out = torch.empty((tokens, features // 2), dtype=torch.bfloat16, device=x.device)
-    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int] + _ROW_SCALE_ARGS + [c_void_p])
-    _check(f(_ptr(out), _ptr(x), _ptr(weight_tiled), tokens, features, K, skinny_gemm_slices(tokens, features, K), *scale, _stream()), "skinny_gemm_swiglu")
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int] + _ROW_SCALE_ARGS + [c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight_tiled), tokens, features, K, skinny_gemm_slices(tokens, features, K), GLU_ACTIVATIONS[activation], *scale,
+             _stream()), "skinny_gemm_swiglu")
     return out
 
 
@@ -762,15 +809,15 @@ def dense_gemm_act(x, weight: torch.Tensor, kind: str) -> torch.Tensor:
     return out
 
 
-def dense_gemm_swiglu(x, weight_tiled: torch.Tensor) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) in the product's epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate
+def dense_gemm_swiglu(x, weight_tiled: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) (act: silu or another of GLU_ACTIVATIONS) in the product's epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate
     rows, then the 64 up rows of the same features.  Returns bfloat16 [tokens, I]."""
     tokens, features, K = _dense_sizes(x, weight_tiled, "dense_gemm_swiglu")
-    if features % 128:
-        raise KernelError("dense_gemm_swiglu: the interleaved layout needs an intermediate size that is a multiple of 64")
+    if features % 128 or activation not in GLU_ACTIVATIONS:
+        raise KernelError("dense_gemm_swiglu: the interleaved layout needs an intermediate size that is a multiple of 64, and a known activation")
     act = torch.empty((tokens, features // 2), dtype=torch.bfloat16, device=x.device)
-    f = _fn("dense_gemm.cu", "dli_dense_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(act), _ptr(x), _ptr(weight_tiled), tokens, features, K, _stream()), "dense_gemm_swiglu")
+    f = _fn("dense_gemm.cu", "dli_dense_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(act), _ptr(x), _ptr(weight_tiled), tokens, features, K, GLU_ACTIVATIONS[activation], _stream()), "dense_gemm_swiglu")
     return act
 
 
@@ -942,6 +989,40 @@ def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor) -> None:
     _check(f(_ptr(out), c_void_p(gate.data_ptr()), gate.stride(0), n, cols, DT_CODE[out.dtype], _stream()), "sigmoid_gate")
 
 
+def latent_prep(q_out: torch.Tensor, proj: torch.Tensor, w_norm: torch.Tensor, eps: float, positions: torch.Tensor,
+                inv_freq: torch.Tensor | None, slots: torch.Tensor | None, k_pool: torch.Tensor | None, num_heads: int, head_dim: int,
+                rot_dim: int, kv_rank: int, rotary_dim: int, page_size: int) -> None:
+    """Between the projections of an attention over a cached latent and its attention kernel, one kernel a step.
+    proj [n, >= nh (d + dr) + r + dr]: per head d plain and dr rotated query numbers, then the down projection: r latent
+    numbers and dr of a key part that all heads share.  The latent is divided by its RMS (``eps`` inside the root) and
+    multiplied by ``w_norm`` [r]; the first ``rotary_dim`` of the dr numbers of the key part and of every head's query part
+    are rotated (rotate-half pairing, angle float32(position) * inv_freq[i]).  The cache row latent | key part goes to
+    ``k_pool`` [pages, 1, page_size, r + dr] at ``slots`` (if given); the rotated query parts go to columns r .. r + dr of
+    every head of ``q_out`` [n, nh (r + dr)], whose other columns this kernel leaves alone."""
+    _need(positions, "positions", torch.int32), _need(q_out, "q_out"), _need(w_norm, "w_norm", torch.float32)
+    if proj.dtype not in DT_CODE or proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda or q_out.dtype != proj.dtype:
+        raise KernelError("latent_prep: proj must be a CUDA matrix with unit column stride, q_out of its dtype")
+    n = proj.shape[0]
+    row = kv_rank + rot_dim
+    if (proj.shape[1] < num_heads * (head_dim + rot_dim) + row or positions.numel() != n or tuple(q_out.shape) != (n, num_heads * row)
+            or w_norm.numel() != kv_rank or rotary_dim % 2 or rotary_dim > rot_dim):
+        raise KernelError("latent_prep: shapes do not agree")
+    if rotary_dim:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("latent_prep: inv_freq must have rotary_dim / 2 entries")
+    write = slots is not None
+    if write:
+        _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", proj.dtype)
+        if tuple(k_pool.shape[1:]) != (1, page_size, row) or slots.numel() != n:
+            raise KernelError("latent_prep: pool layout must be [pages, 1, page_size, kv_rank + rot_dim]")
+    f = _fn("attention_prep.cu", "dli_latent_prep",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_void_p])
+    _check(f(_ptr(q_out), _ptr(proj), proj.stride(0), _ptr(w_norm), eps, _ptr(positions), _ptr(inv_freq if rotary_dim else None),
+             _ptr(slots if write else None), _ptr(k_pool if write else None), n, num_heads, head_dim, rot_dim, kv_rank, rotary_dim, page_size,
+             DT_CODE[proj.dtype], _stream()), "latent_prep")
+
+
 # ------------------------------------------------------------------ state-space mixer
 
 
@@ -1006,12 +1087,44 @@ def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, d
              _ptr(state_slot), state_slot.numel(), heads, P, N, groups, int(max_len), DT_CODE[u.dtype], _stream()), "ssm_scan")
 
 
-def gated_group_rmsnorm(out: torch.Tensor, y: torch.Tensor, u: torch.Tensor, z_col: int, weight: torch.Tensor, parts: int, eps: float) -> None:
+def gated_group_rmsnorm(out: torch.Tensor, y: torch.Tensor, u: torch.Tensor, z_col: int, weight: torch.Tensor, parts: int, eps: float,
+                        gate_after: bool = False) -> None:
     """out = g / sqrt(mean(g^2) + eps) * weight with g = y * silu(z), the mean taken over each of ``parts`` equal runs
-    of the row; z is columns z_col .. of u; y float32."""
+    of the row; z is columns z_col .. of u; y float32.  ``gate_after``: the gate stays out of the norm,
+    out = y / sqrt(mean(y^2) + eps) * weight * silu(z)."""
     _columns(u, "gated_group_rmsnorm"), _need(out, "out", u.dtype), _need(y, "y", torch.float32), _need(weight, "weight", torch.float32)
     n, inner = y.shape
     if tuple(out.shape) != (n, inner) or u.shape[0] != n or z_col + inner > u.shape[1] or weight.numel() != inner or inner % parts:
         raise KernelError("gated_group_rmsnorm: shapes do not agree")
-    f = _fn("ssm.cu", "dli_gated_group_rmsnorm", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
-    _check(f(_ptr(out), _ptr(y), _ptr(u), u.stride(0), z_col, _ptr(weight), n, inner, parts, eps, DT_CODE[u.dtype], _stream()), "gated_group_rmsnorm")
+    f = _fn("ssm.cu", "dli_gated_group_rmsnorm", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(y), _ptr(u), u.stride(0), z_col, _ptr(weight), n, inner, parts, eps, int(gate_after), DT_CODE[u.dtype], _stream()),
+           "gated_group_rmsnorm")
+
+
+# ------------------------------------------------------------------ gated delta rule
+
+DELTA_MAX_HEAD_DIM = 256
+
+
+def delta_rule_scan(o: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: int, a_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                    state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, kv_heads: int, head_dim: int, unit_eps: float,
+                    max_len: int = 1 << 30) -> None:
+    """The gated delta rule over every sequence's tokens of this step, from and to its slot of ``state``
+    [slots, heads, dv, d] (float32; S transposed, so that a value column's d numbers are contiguous).
+    qkv [n, 2 kv_heads d + heads dv] holds q | k | v after convolution and activation; b and a are columns b_col + head and
+    a_col + head of u.  Per head h (q/k head h // (heads / kv_heads)): q and k are divided by sqrt(sum of squares + unit_eps),
+    q also by sqrt(d); beta = sigmoid(b), gamma = exp(-exp(a_log) softplus(a + dt_bias));
+    S <- gamma S, w = beta (v - S^T k), S <- S + k w^T, o = S^T q.  o [n, heads dv] float32."""
+    _columns(u, "delta_rule_scan"), _need(qkv, "qkv", u.dtype), _need(o, "o", torch.float32), _need(state, "state", torch.float32)
+    _need(dt_bias, "dt_bias", torch.float32), _need(a_log, "a_log", torch.float32)
+    _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
+    _, heads, dv, d = state.shape
+    n = qkv.shape[0]
+    if (d != head_dim or kv_heads < 1 or heads % kv_heads or qkv.shape[1] != 2 * kv_heads * d + heads * dv or tuple(o.shape) != (n, heads * dv)
+            or u.shape[0] != n or b_col + heads > u.shape[1] or a_col + heads > u.shape[1] or d > DELTA_MAX_HEAD_DIM
+            or dt_bias.numel() != heads or a_log.numel() != heads or q_start.numel() != state_slot.numel() + 1):
+        raise KernelError(f"delta_rule_scan: shapes do not agree (or the head size is above {DELTA_MAX_HEAD_DIM})")
+    f = _fn("delta_rule.cu", "dli_delta_rule_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                     c_void_p] + [c_int] * 6 + [c_float, c_int, c_void_p])
+    _check(f(_ptr(o), _ptr(qkv), _ptr(u), u.stride(0), b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(q_start), _ptr(state_slot),
+             state_slot.numel(), heads, kv_heads, d, dv, int(max_len), unit_eps, DT_CODE[u.dtype], _stream()), "delta_rule_scan")

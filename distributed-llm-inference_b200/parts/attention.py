@@ -1,4 +1,4 @@
-"""Grouped-query attention over the paged cache."""
+"""Attention over the paged cache: grouped-query, with a sink, and over a cached latent."""
 
 from __future__ import annotations
 
@@ -7,7 +7,7 @@ import torch
 from ..cache.needs import PagedKVNeed
 from ..kernels import attention as attn_kernels
 from ..kernels import ops
-from ..kernels.gemm import last_product, project
+from ..kernels.gemm import heads_product, last_product, project
 from ..weights.loader import TensorDecl
 from .base import Part, build_part, register_part, tensor_name
 
@@ -164,4 +164,97 @@ class SinkAttention(Part):
                                      sink=self.sink)
         if self.gated:
             ops.sigmoid_gate(out, proj[:, self.gate_col : self.gate_col + self.nh * self.d])
+        return project(out, self.wo)
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Part):
+    """Attention whose keys and values are both made from one small cached vector per token (a latent).
+
+    The down projection yields ``kv_rank`` numbers, RMS-normed with a plain weight: the latent c, and — when
+    ``rot_dim`` > 0 — ``rot_dim`` more, one key part that is rotated by the token's position and shared by all heads.
+    Head a's keys are W_uk[a] c (``head_dim`` numbers) followed by the rotated part, its values W_uv[a] c
+    (``value_dim`` numbers); its queries are laid out the same way, [head_dim plain | rot_dim rotated].  Only c and the
+    rotated key part are cached: one row of kv_rank + rot_dim numbers per token, one "KV head".
+
+    The up projections are never applied to the cache.  Since q . (W_uk c) = (W_uk^T q) . c, each head's plain query
+    is carried into the latent space (a product of head_dim x kv_rank per head) and the framework's paged attention
+    kernels run as multi-query attention over the cached rows, the values being the rows' first kv_rank numbers; the
+    weighted sum of latents then goes through W_uv head by head.  Causal, with an optional sliding ``window``; with
+    ``gate`` the concatenated heads are multiplied by sigmoid(W_g x) before the output projection.
+
+    One product yields q | down | g; one kernel norms the latent, rotates, writes the cache row and places the rotated
+    query parts behind the latent-space queries.
+    params: hidden_size, num_heads, head_dim, rot_dim, value_dim, kv_rank, scale, window, gate, eps, rotary_dim (how
+    many of the rot_dim dimensions are rotated, rotate-half pairing), theta, tensors (names of q, dkv, dkv_norm, uk,
+    uv, g, o)."""
+
+    graph_capturable = True
+    takes_scaled_rows = False
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.d, self.dr = int(p["num_heads"]), int(p["head_dim"]), int(p.get("rot_dim") or 0)
+        self.dv, self.rank = int(p["value_dim"]), int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.window = p.get("window")
+        self.gated = bool(p.get("gate", False))
+        self.eps = float(p["eps"])
+        self.rotary_dim = int(p.get("rotary_dim", self.dr)) if self.dr else 0
+        if self.rotary_dim % 2 or self.rotary_dim > self.dr:
+            raise ValueError(f"rotary_dim={self.rotary_dim} must be even and at most rot_dim={self.dr}")
+        self.row = self.rank + self.dr  # what a token keeps in the cache, and the size of a query in the latent space
+        self.inv_freq = None
+        if self.rotary_dim:
+            from .rotary import inverse_frequencies
+
+            self.inv_freq = inverse_frequencies({"rotary_dim": self.rotary_dim, "theta": float(p["theta"])}).to(env.device)
+        self.names = {role: tensor_name(spec, role, default) for role, default in (
+            ("q", "q_proj.weight"), ("dkv", "kv_down_proj.weight"), ("dkv_norm", "kv_norm.weight"), ("uk", "k_up_proj.weight"),
+            ("uv", "v_up_proj.weight"), ("g", "g_proj.weight"), ("o", "o_proj.weight"))}
+        self.q_cols = self.nh * (self.d + self.dr)
+        self.gate_col = self.q_cols + self.row
+        self.w_in = self.w_uk = self.w_uv = self.wo = self.w_norm = None
+
+    def declare(self):
+        H, nm = self.hidden, self.names
+        out = {nm["q"]: TensorDecl((self.q_cols, H)), nm["dkv"]: TensorDecl((self.row, H)),
+               nm["dkv_norm"]: TensorDecl((self.rank,), "vector32"), nm["uk"]: TensorDecl((self.nh * self.d, self.rank)),
+               nm["uv"]: TensorDecl((self.nh * self.dv, self.rank)), nm["o"]: TensorDecl((H, self.nh * self.dv))}
+        if self.gated:
+            out[nm["g"]] = TensorDecl((self.nh * self.dv, H))
+        return out
+
+    def load(self, tensors):
+        nm = self.names
+        rows = [tensors[nm["q"]], tensors[nm["dkv"]]] + ([tensors[nm["g"]]] if self.gated else [])
+        self.w_in = torch.cat(rows, 0).contiguous()
+        self.w_uk = tensors[nm["uk"]].view(self.nh, self.d, self.rank)  # q_latent[a] = q_plain[a] W_uk[a]
+        self.w_uv = tensors[nm["uv"]].view(self.nh, self.dv, self.rank).transpose(1, 2)  # o[a] = o_latent[a] W_uv[a]^T
+        self.wo, self.w_norm = tensors[nm["o"]], tensors[nm["dkv_norm"]]
+
+    def cache_need(self):
+        return PagedKVNeed(1, self.row, self.window, values_in_keys=True)
+
+    def decode_launch_key(self, num_seqs: int, max_kv_len: int, page_size: int):
+        return attn_kernels.decode_splits(num_seqs, self.nh, 1, self.row, page_size, max_kv_len)
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        n = x.shape[0]
+        proj = project(x, self.w_in)
+        group = batch.group(cache.group)
+        # the latent-space queries [n, heads, kv_rank + rot_dim]: the kernel fills the rotated tails, the product the rest
+        q = torch.empty((n, self.nh * self.row), dtype=x.dtype, device=x.device)
+        ops.latent_prep(q, proj, self.w_norm, self.eps, batch.positions, self.inv_freq, group.slots if cache.writes else None,
+                        cache.k if cache.writes else None, self.nh, self.d, self.dr, self.rank, self.rotary_dim, cache.page_size)
+        heads_product(proj[:, : self.q_cols].view(n, self.nh, self.d + self.dr)[:, :, : self.d], self.w_uk,
+                      q.view(n, self.nh, self.row)[:, :, : self.rank])
+        latent = torch.empty((n, self.nh * self.row), dtype=x.dtype, device=x.device)
+        attn_kernels.paged_attention(latent, q, cache, batch, self.nh, self.scale, self.window, splits=batch.launch_keys.get(id(self)))
+        out = torch.empty((n, self.nh * self.dv), dtype=x.dtype, device=x.device)
+        heads_product(latent.view(n, self.nh, self.row)[:, :, : self.rank], self.w_uv, out.view(n, self.nh, self.dv))
+        if self.gated:
+            ops.sigmoid_gate(out, proj[:, self.gate_col : self.gate_col + self.nh * self.dv])
         return project(out, self.wo)

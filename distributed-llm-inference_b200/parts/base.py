@@ -45,6 +45,9 @@ these is served with plain tensors:
 * an arrangement with ``first_consumer() -> (norm, part)`` and ``defer_last_product(flag)`` lets
   the model extend this across layer borders.
 
+The outputs of two branches that run side by side stay pending as ``PendingSum(a, b)``; a norm with
+``takes_pending_sum`` adds both in its own kernel, any other reader has them settled first.
+
 A sublayer's output that is normed before the residual addition stays pending as ``PendingNormed(a, norm)``:
 a norm with ``post_add_norm(h, a, post, rows=None) -> y`` (h += post(a); y = norm(h), one kernel) takes it as
 it is; any other reader gets it settled first (``post.add_into(h, a)``).
@@ -125,6 +128,20 @@ class PendingNormed:
         self.a, self.norm = a, norm
 
 
+class PendingSum:
+    """Two sublayer outputs ``a`` and ``b`` (activation dtype; ``b`` may be None) that are still to be added to the
+    residual stream, as (a + b) in float32: the branches of a layer that run side by side.  A norm whose ``add_norm``
+    takes it adds both in its own kernel."""
+
+    __slots__ = ("a", "b")
+
+    def __init__(self, a: torch.Tensor, b: torch.Tensor | None) -> None:
+        self.a, self.b = a, b
+
+    def total(self) -> torch.Tensor:
+        return self.a.float() if self.b is None else self.a.float() + self.b.float()
+
+
 class ResidualStream:
     """The float32 residual h [n, H] and a delta (activation dtype) not yet added to it.
     Keeping the delta pending lets the next norm do the addition in the same kernel.  ``pending``
@@ -152,6 +169,8 @@ class ResidualStream:
         delta, self._pending = self._pending, None
         if isinstance(delta, PendingNormed):
             delta.norm.add_into(self.h, delta.a)
+        elif isinstance(delta, PendingSum):
+            self.h += delta.total()
         elif delta is not None:
             self.h += (delta.materialize() if isinstance(delta, PendingProduct) else delta).float()
         return self.h
@@ -173,6 +192,9 @@ def normed_input(norm, h: torch.Tensor, delta, consumer, rows: torch.Tensor | No
         if rows is not None:
             raise TypeError("a normed delta that is still pending can only be read row by row by a norm with post_add_norm")
         delta.norm.add_into(h, delta.a)
+        delta = None
+    if isinstance(delta, PendingSum) and not getattr(norm, "takes_pending_sum", False):
+        h += delta.total()
         delta = None
     if isinstance(delta, PendingProduct):
         if rows is None and can_fuse(norm, consumer):

@@ -2,7 +2,9 @@
 
 from __future__ import annotations
 
-from .base import BuildEnv, Part, PendingNormed, ResidualStream, build_part, can_fuse, normed_input, register_part
+import torch
+
+from .base import BuildEnv, Part, PendingNormed, PendingSum, ResidualStream, build_part, can_fuse, normed_input, register_part
 
 
 @register_part("arrangement", "prenorm")
@@ -84,3 +86,44 @@ class SandwichBlock(Part):
             y = normed_input(self.ffn_norm, stream.h, pending, self.ffn)
             pending = PendingNormed(self.ffn.forward(y), self.ffn_post_norm)
         stream.pending = pending
+
+
+@register_part("arrangement", "parallel")
+class ParallelBlock(Part):
+    """x = x + (mixer(norm_a(x)) + ffn(norm_f(x))): both branches read the same x, each behind a norm of its own, and
+    their outputs are added to the stream together.  Roles: mixer_norm, mixer, and — a layer may have no
+    feed-forward — ffn_norm, ffn.  The two outputs stay pending on the stream as a ``PendingSum``; the norm in front
+    of the next layer's branches adds them, and where both norms divide by the same root mean square
+    (``add_norm_pair``) one kernel adds the pending outputs and writes both branches' inputs."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env: BuildEnv) -> None:
+        self.spec, self.env = spec, env
+        self.mixer_norm = build_part("norm", spec.parts["mixer_norm"], env)
+        self.mixer = build_part("mixer", spec.parts["mixer"], env)
+        self.has_ffn = "ffn" in spec.parts
+        if self.has_ffn:
+            self.ffn_norm = build_part("norm", spec.parts["ffn_norm"], env)
+            self.ffn = build_part("feed_forward", spec.parts["ffn"], env)
+
+    def children(self):
+        return [self.mixer_norm, self.mixer] + ([self.ffn_norm, self.ffn] if self.has_ffn else [])
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, stream: ResidualStream, batch, cache) -> None:
+        pair = getattr(self.mixer_norm, "add_norm_pair", None) if self.has_ffn else None
+        if pair is not None and not isinstance(stream.take_pending(), (PendingSum, torch.Tensor, type(None))):
+            stream.settle()
+        ys = pair(stream.h, stream.take_pending(), self.ffn_norm) if pair is not None else None
+        if ys is not None:
+            stream.pending = None
+            ya, yf = ys
+        else:
+            ya = normed_input(self.mixer_norm, stream.h, stream.take_pending(), self.mixer)
+            stream.pending = None  # the norm has added it; the second norm reads the same sum
+            yf = normed_input(self.ffn_norm, stream.h, None, self.ffn) if self.has_ffn else None
+        a = self.mixer.forward(ya, batch, cache)
+        stream.pending = PendingSum(a, self.ffn.forward(yf) if self.has_ffn else None)

@@ -1,4 +1,4 @@
-"""SwiGLU feed-forward."""
+"""Feed-forwards: gated (SwiGLU and its kin) and plain."""
 
 from __future__ import annotations
 
@@ -10,13 +10,14 @@ from ..weights.loader import TensorDecl
 from .base import Part, register_part, tensor_name
 
 
+@register_part("feed_forward", "glu")
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
-    """down(silu(gate(x)) * up(x)) (src/dli/model/llama.py:189-191).  gate and up are read by
-    their own names and laid together at load, so one product yields both: side by side, or —
-    when the intermediate size is a multiple of 64 — interleaved in blocks of 64 rows, the layout
-    in which the decode product applies SiLU(gate) * up in its own epilogue.
-    params: hidden_size, intermediate_size."""
+    """down(act(gate(x)) * up(x)), act = SiLU (src/dli/model/llama.py:189-191) or another activation of
+    ``ops.GLU_ACTIVATIONS``.  gate and up are read by their own names and laid together at load, so one
+    product yields both: side by side, or — when the intermediate size is a multiple of 64 — interleaved in
+    blocks of 64 rows, the layout in which the decode product applies act(gate) * up in its own epilogue.
+    params: hidden_size, intermediate_size, activation (default ``silu``), tensors (names of gate, up, down)."""
 
     graph_capturable = True
     takes_scaled_rows = True  # the input only goes to the gate | up product
@@ -26,38 +27,41 @@ class SwiGLU(Part):
         super().__init__(spec, env)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        self.activation = spec.params.get("activation", "silu")
+        if self.activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not supported (known: {sorted(ops.GLU_ACTIVATIONS)})")
+        self.names = {role: tensor_name(spec, role, role + "_proj.weight") for role in ("gate", "up", "down")}
         self.w_gate_up: torch.Tensor | None = None
         self.tiled = False
         self.w_down: torch.Tensor | None = None
 
     def declare(self):
-        px = self.spec.prefix
+        nm = self.names
         return {
-            px + "gate_proj.weight": TensorDecl((self.inter, self.hidden)),
-            px + "up_proj.weight": TensorDecl((self.inter, self.hidden)),
-            px + "down_proj.weight": TensorDecl((self.hidden, self.inter)),
+            nm["gate"]: TensorDecl((self.inter, self.hidden)),
+            nm["up"]: TensorDecl((self.inter, self.hidden)),
+            nm["down"]: TensorDecl((self.hidden, self.inter)),
         }
 
     def load(self, tensors):
-        px = self.spec.prefix
-        gate, up = tensors[px + "gate_proj.weight"], tensors[px + "up_proj.weight"]
+        gate, up = tensors[self.names["gate"]], tensors[self.names["up"]]
         self.tiled = self.inter % 64 == 0 and self.env.dtype == torch.bfloat16
         if self.tiled:
             blocks = self.inter // 64
             self.w_gate_up = torch.stack([gate.view(blocks, 64, self.hidden), up.view(blocks, 64, self.hidden)], 1).reshape(2 * self.inter, self.hidden).contiguous()
         else:
             self.w_gate_up = torch.cat([gate, up], 0).contiguous()
-        self.w_down = tensors[px + "down_proj.weight"]
+        self.w_down = tensors[self.names["down"]]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tiled and fused_epilogue(x):
-            act = ops.skinny_gemm_swiglu(x, self.w_gate_up)
+            act = ops.skinny_gemm_swiglu(x, self.w_gate_up, self.activation)
         elif self.tiled and dense_product(x, 2 * self.inter, "swiglu"):
-            act = ops.dense_gemm_swiglu(x, self.w_gate_up)
+            act = ops.dense_gemm_swiglu(x, self.w_gate_up, self.activation)
         else:
             gate_up = project(x, self.w_gate_up)
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-            ops.silu_mul(act, gate_up, self.tiled)
+            ops.silu_mul(act, gate_up, self.tiled, self.activation)
         return last_product(act, self.w_down, self.defer_output)
 
 

@@ -39,8 +39,9 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     """logits = y W^T in float32, W the embedding matrix when ``tied_to`` names it
     (src/dli/model/llama.py:304-305).  A tied checkpoint that stores the head anyway is
-    accepted if both are equal (src/dli/model/loader.py:75-80).
-    params: vocab_size, hidden_size, tied_to."""
+    accepted if both are equal (src/dli/model/loader.py:75-80).  With ``scale`` the logits are multiplied by it, and
+    with ``softcap`` (a positive number c) then bent into (-c, c): c * tanh(logits / c); both in float32, one kernel.
+    params: vocab_size, hidden_size, tied_to, scale, softcap."""
 
     graph_capturable = True
     takes_scaled_rows = True
@@ -49,6 +50,8 @@ class LMHead(Part):
         super().__init__(spec, env)
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
         self.tied_to = spec.params.get("tied_to")
+        self.scale = float(spec.params.get("scale") or 1.0)
+        self.softcap = float(spec.params.get("softcap") or 0.0)
         self.name = tensor_name(spec, "weight", "weight")
         self.weight: torch.Tensor | None = None
 
@@ -59,7 +62,10 @@ class LMHead(Part):
         self.weight = tensors[self.tied_to or self.name]
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
-        return project(y, self.weight, out_dtype=torch.float32, max_tokens=SKINNY_MAX_TOKENS_HEAD)
+        logits = project(y, self.weight, out_dtype=torch.float32, max_tokens=SKINNY_MAX_TOKENS_HEAD)
+        if self.scale != 1.0 or self.softcap:
+            ops.scale_softcap(logits, self.scale, self.softcap)
+        return logits
 
 
 def _walk(part) -> list[Part]:

@@ -6,34 +6,58 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import Part, register_part, tensor_name
+from .base import Part, PendingSum, register_part, tensor_name
 
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     """y = (h + delta) * rsqrt(mean((h + delta)^2) + eps) * weight, all in float32 and rounded
     once (src/dli/model/llama.py:41-44 rounds before the weight product; one rounding is closer
-    to the float32 result).  params: size, eps."""
+    to the float32 result).  params: size, eps, tensor (the weight's name; default prefix + "weight"),
+    offset (added to the stored weight at load: 1.0 for checkpoints that store the deviation from one).
+
+    ``delta`` may be a ``PendingSum`` of two sublayer outputs (layers whose branches run side by side): both are
+    added in the same kernel.  ``add_norm_pair`` also norms the same sum with a second norm's weight — two readers
+    of one stream share the sum of squares."""
 
     graph_capturable = True
+    takes_pending_sum = True
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.offset = float(spec.params.get("offset", 0.0))
+        self.name = tensor_name(spec, "weight", "weight")
         self.weight: torch.Tensor | None = None
 
     def declare(self):
-        return {self.spec.prefix + "weight": TensorDecl((self.size,), "vector32")}
+        return {self.name: TensorDecl((self.size,), "vector32")}
 
     def load(self, tensors):
-        self.weight = tensors[self.spec.prefix + "weight"]
+        self.weight = tensors[self.name] + self.offset if self.offset else tensors[self.name]
 
-    def add_norm(self, h: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    def _out(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
         n = h.shape[0] if rows is None else rows.numel()
-        y = torch.empty((n, self.size), dtype=self.env.dtype, device=h.device)
-        ops.add_rmsnorm(y, h, delta, self.weight, self.eps, rows)
+        return torch.empty((n, self.size), dtype=self.env.dtype, device=h.device)
+
+    def add_norm(self, h: torch.Tensor, delta, rows: torch.Tensor | None = None) -> torch.Tensor:
+        y = self._out(h, rows)
+        if isinstance(delta, PendingSum):
+            ops.add_rmsnorm_pair(y, None, h, delta.a, delta.b, self.weight, None, self.eps, rows)
+        else:
+            ops.add_rmsnorm(y, h, delta, self.weight, self.eps, rows)
         return y
+
+    def add_norm_pair(self, h: torch.Tensor, delta, other: "RMSNorm") -> tuple[torch.Tensor, torch.Tensor] | None:
+        """(self(h + delta), other(h + delta)) from one kernel, the sum written back to h; None if ``other`` does not
+        divide by the same root mean square."""
+        if not isinstance(other, RMSNorm) or other.eps != self.eps or other.size != self.size:
+            return None
+        y1, y2 = self._out(h, None), self._out(h, None)
+        a, b = (delta.a, delta.b) if isinstance(delta, PendingSum) else (delta, None)
+        ops.add_rmsnorm_pair(y1, y2, h, a, b, self.weight, other.weight, self.eps, None)
+        return y1, y2
 
     def add_product_norm(self, h: torch.Tensor, product) -> ops.ScaledRows | None:
         """h += product (computed here, float32 sums added to float32 h) and the norm's first half

@@ -1,4 +1,4 @@
-"""State-space mixers: per-request state of fixed size instead of keys and values in pages."""
+"""Recurrent mixers (state-space, delta rule): per-request state of fixed size instead of keys and values in pages."""
 
 from __future__ import annotations
 
@@ -84,4 +84,92 @@ class Mamba2Mixer(Part):
                      self.groups, max_len=batch.max_q_len)
         gated = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         ops.gated_group_rmsnorm(gated, y, u, 0, w["norm"], self.parts, self.eps)
+        return project(gated, w["o"])
+
+
+@register_part("mixer", "gated_delta")
+class GatedDeltaRule(Part):
+    """The gated delta rule on any mix of prompt portions and decoded tokens: a linear recurrence whose state is a
+    matrix S (head_dim x value_dim) per head.
+
+    One product yields q | k | v | g | b | a (q and k: ``num_kv_heads`` heads of ``head_dim``; v and g: ``num_heads``
+    heads of ``value_dim``; b and a: one number per head).  q | k | v pass a causal convolution per channel
+    (``conv_taps`` taps, no bias) and SiLU; q and k are then made unit vectors per head (float32; ``unit_eps`` inside
+    the root) and q is multiplied by head_dim^-1/2.  Head h reads q/k head h // (num_heads / num_kv_heads).  Per head
+    and token, with beta = sigmoid(b) and the decay gamma = exp(-exp(A_log) softplus(a + dt_bias)):
+
+        S <- gamma S;    u = beta (v - S^T k);    S <- S + k u^T;    o = S^T q
+
+    (the read-out sees the token's own write).  Each head's o is divided by its root mean square (``eps``), multiplied
+    by a weight of ``value_dim`` numbers that the heads share and by silu(g), and goes through the output projection.
+    A request keeps S (float32) and the convolution's last taps - 1 inputs in its state slot; both start at zero.
+
+    params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, conv_taps, eps, unit_eps, tensors (names of q,
+    k, v, b, a, g, o, A_log, dt_bias, norm, q_conv, k_conv, v_conv)."""
+
+    graph_capturable = True  # padding rows of a replayed graph name a state slot that no request owns
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.kv_heads = int(p["num_heads"]), int(p["num_kv_heads"])
+        self.d, self.dv, self.taps = int(p["head_dim"]), int(p["value_dim"]), int(p["conv_taps"])
+        self.eps, self.unit_eps = float(p["eps"]), float(p.get("unit_eps", 1e-6))
+        if self.heads % self.kv_heads or self.taps < 1:
+            raise ValueError("gated_delta: num_heads must be a multiple of num_kv_heads, and conv_taps >= 1")
+        if self.d > ops.DELTA_MAX_HEAD_DIM:
+            raise ValueError(f"gated_delta: head_dim={self.d} is above the scan kernel's {ops.DELTA_MAX_HEAD_DIM}")
+        self.qk, self.inner = self.kv_heads * self.d, self.heads * self.dv
+        self.channels = 2 * self.qk + self.inner  # what passes the convolution: q | k | v
+        self.g_col = self.channels
+        self.b_col = self.g_col + self.inner
+        self.a_col = self.b_col + self.heads
+        defaults = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "b": "b_proj.weight", "a": "a_proj.weight",
+                    "g": "g_proj.weight", "o": "o_proj.weight", "A_log": "A_log", "dt_bias": "dt_bias", "norm": "norm.weight",
+                    "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight"}
+        self.names = {role: tensor_name(spec, role, default) for role, default in defaults.items()}
+        self.w: dict[str, torch.Tensor] = {}
+
+    def declare(self):
+        nm, H = self.names, self.hidden
+        return {
+            nm["q"]: TensorDecl((self.qk, H)), nm["k"]: TensorDecl((self.qk, H)), nm["v"]: TensorDecl((self.inner, H)),
+            nm["g"]: TensorDecl((self.inner, H)), nm["b"]: TensorDecl((self.heads, H)), nm["a"]: TensorDecl((self.heads, H)),
+            nm["o"]: TensorDecl((H, self.inner)),
+            nm["q_conv"]: TensorDecl((self.qk, self.taps), "vector32"), nm["k_conv"]: TensorDecl((self.qk, self.taps), "vector32"),
+            nm["v_conv"]: TensorDecl((self.inner, self.taps), "vector32"),
+            nm["A_log"]: TensorDecl((self.heads,), "vector32"), nm["dt_bias"]: TensorDecl((self.heads,), "vector32"),
+            nm["norm"]: TensorDecl((self.dv,), "vector32"),
+        }
+
+    def load(self, tensors):
+        t = {role: tensors[name] for role, name in self.names.items()}
+        self.w = {
+            "in": torch.cat([t["q"], t["k"], t["v"], t["g"], t["b"], t["a"]], 0).contiguous(),
+            # [taps, channels]: the kernel reads a tap's weights side by side
+            "conv": torch.cat([t["q_conv"], t["k_conv"], t["v_conv"]], 0).t().contiguous(),
+            "A_log": t["A_log"], "dt_bias": t["dt_bias"], "o": t["o"],
+            "norm": t["norm"].repeat(self.heads).contiguous(),  # the heads share the weight; the kernel reads one per column
+        }
+
+    def cache_need(self):
+        """The recurrent state (float32; kept transposed, a value column's head_dim numbers together) and the
+        convolution's carried inputs (activation dtype), per request."""
+        return (StateNeed((self.heads, self.dv, self.d), torch.float32), StateNeed((self.taps - 1, self.channels), self.env.dtype))
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        w = self.w
+        n = x.shape[0]
+        state, conv_state = cache.states
+        u = project(x, w["in"])  # q | k | v | g | b | a
+        qkv = torch.empty((n, self.channels), dtype=x.dtype, device=x.device)
+        ops.causal_conv_silu(qkv, u, 0, w["conv"], None, conv_state, batch.seq_of_token, batch.q_start, batch.state_slot)
+        if self.taps > 1:
+            ops.conv_state_update(conv_state, u, 0, batch.q_start, batch.state_slot)
+        o = torch.empty((n, self.inner), dtype=torch.float32, device=x.device)
+        ops.delta_rule_scan(o, qkv, u, self.b_col, self.a_col, w["dt_bias"], w["A_log"], state, batch.q_start, batch.state_slot,
+                            self.kv_heads, self.d, self.unit_eps, max_len=batch.max_q_len)
+        gated = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
+        ops.gated_group_rmsnorm(gated, o, u, self.g_col, w["norm"], self.heads, self.eps, gate_after=True)
         return project(gated, w["o"])

@@ -67,7 +67,11 @@ def rotary_store(qkv, positions, inv_freq, slots, k_pool, v_pool, num_heads, num
         v_pool[page, :, off, :] = heads[:, num_heads + num_kv_heads :]
 
 
-def silu_mul(out, gate_up, tiled=False):
+def _gelu_tanh(z):
+    return 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z**3)))
+
+
+def silu_mul(out, gate_up, tiled=False, activation="silu"):
     n, inter = out.shape
     if tiled:
         blocks = gate_up.view(n, inter // 64, 2, 64)
@@ -75,7 +79,27 @@ def silu_mul(out, gate_up, tiled=False):
     else:
         gate, up = gate_up[:, :inter], gate_up[:, inter:]
     g = gate.float()
-    out.copy_((g / (1 + torch.exp(-g)) * up.float()).to(out.dtype))
+    act = g / (1 + torch.exp(-g)) if activation == "silu" else _gelu_tanh(g)
+    out.copy_((act * up.float()).to(out.dtype))
+
+
+def add_rmsnorm_pair(y1, y2, h, a, b, w1, w2, eps, rows=None):
+    idx = slice(None) if rows is None else rows.long()
+    x = h[idx]
+    if a is not None or b is not None:
+        x = x + ((a[idx].float() if a is not None else 0.0) + (b[idx].float() if b is not None else 0.0))
+        if rows is None:
+            h.copy_(x)
+    unit = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
+    y1.copy_((unit * w1).to(y1.dtype))
+    if y2 is not None:
+        y2.copy_((unit * w2).to(y2.dtype))
+
+
+def scale_softcap(logits, scale, cap):
+    logits *= scale
+    if cap > 0:
+        logits.copy_(cap * torch.tanh(logits / cap))
 
 
 def paged_attention_simt(out, qkv, k_pool, v_pool, block_tables, seq_of_token, positions, num_heads, scale, window=None, sink=None):
@@ -200,6 +224,26 @@ def qk_norm_rotary_store(proj, wq, wk, eps, positions, inv_freq, slots, k_pool, 
     return qk[:, :num_heads].reshape(n, nq).to(proj.dtype)
 
 
+def latent_prep(q_out, proj, w_norm, eps, positions, inv_freq, slots, k_pool, num_heads, head_dim, rot_dim, kv_rank, rotary_dim, page_size):
+    n = proj.shape[0]
+    qc = num_heads * (head_dim + rot_dim)
+    down = proj[:, qc : qc + kv_rank + rot_dim].float()
+    c = down[:, :kv_rank]
+    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * w_norm
+    turn = torch.cat([proj[:, :qc].float().view(n, num_heads, head_dim + rot_dim)[:, :, head_dim:], down[:, None, kv_rank:]], 1).clone()
+    if rotary_dim:
+        half = rotary_dim // 2
+        ang = positions.float()[:, None] * inv_freq[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        lo, hi = turn[..., :half].clone(), turn[..., half:rotary_dim].clone()
+        turn[..., :half] = lo * cos - hi * sin
+        turn[..., half:rotary_dim] = hi * cos + lo * sin
+    q_out.view(n, num_heads, kv_rank + rot_dim)[:, :, kv_rank:] = turn[:, :num_heads].to(q_out.dtype)
+    if slots is not None:
+        page, off = (slots // page_size).long(), (slots % page_size).long()
+        k_pool[page, 0, off, :] = torch.cat([c, turn[:, num_heads]], -1).to(k_pool.dtype)
+
+
 def sigmoid_gate(out, gate):
     out.copy_((out.float() * torch.sigmoid(gate.float())).to(out.dtype))
 
@@ -248,11 +292,33 @@ def ssm_scan(y, xbc, u, dt_col, dt_bias, a_log, d_skip, state, q_start, state_sl
             y[t] = (torch.einsum("hpn,hn->hp", state[slot], C) + d_skip[:, None] * x).reshape(-1)
 
 
-def gated_group_rmsnorm(out, y, u, z_col, weight, parts, eps):
+def gated_group_rmsnorm(out, y, u, z_col, weight, parts, eps, gate_after=False):
     n, inner = y.shape
-    g = (y * _silu(u[:, z_col : z_col + inner].float())).view(n, parts, inner // parts)
+    gate = _silu(u[:, z_col : z_col + inner].float())
+    g = (y if gate_after else y * gate).view(n, parts, inner // parts)
     g = g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)
-    out.copy_((g.view(n, inner) * weight).to(out.dtype))
+    out.copy_((g.view(n, inner) * weight * (gate if gate_after else 1.0)).to(out.dtype))
+
+
+def delta_rule_scan(o, qkv, u, b_col, a_col, dt_bias, a_log, state, q_start, state_slot, kv_heads, head_dim, unit_eps, max_len=0):
+    _, heads, dv, d = state.shape  # the state is kept transposed: [slot, head, value column, key row]
+    qk = kv_heads * d
+    fan = heads // kv_heads
+    for s in range(state_slot.numel()):
+        slot = int(state_slot[s])
+        for t in range(int(q_start[s]), int(q_start[s + 1])):
+            q = qkv[t, :qk].float().view(kv_heads, d)
+            k = qkv[t, qk : 2 * qk].float().view(kv_heads, d)
+            v = qkv[t, 2 * qk :].float().view(heads, dv)
+            q = (q * torch.rsqrt((q * q).sum(-1, keepdim=True) + unit_eps) * d**-0.5).repeat_interleave(fan, 0)
+            k = (k * torch.rsqrt((k * k).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(fan, 0)
+            beta = torch.sigmoid(u[t, b_col : b_col + heads].float())
+            gamma = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(u[t, a_col : a_col + heads].float() + dt_bias, threshold=20.0))
+            S = state[slot] * gamma[:, None, None]
+            w = beta[:, None] * (v - torch.einsum("hvd,hd->hv", S, k))
+            S = S + w[:, :, None] * k[:, None, :]
+            state[slot] = S
+            o[t] = torch.einsum("hvd,hd->hv", S, q).reshape(-1)
 
 
 # ---- the decode matrix product and its epilogues (bfloat16 in, float32 sums)
@@ -287,10 +353,10 @@ def skinny_gemm_residual(x, weight, h, gain, eps, slices=None):
     return ops.ScaledRows((h * gain).to(torch.bfloat16), sq.view(tokens, tiles, 128).sum(-1), eps)
 
 
-def skinny_gemm_swiglu(x, weight_tiled):
+def skinny_gemm_swiglu(x, weight_tiled, activation="silu"):
     y = _sums(x, weight_tiled)
     out = torch.empty((y.shape[0], y.shape[1] // 2), dtype=torch.bfloat16)
-    silu_mul(out, y, tiled=True)
+    silu_mul(out, y, tiled=True, activation=activation)
     return out
 
 
@@ -320,8 +386,8 @@ def dense_gemm_act(x, weight, kind):
     return skinny_gemm_act(x, weight, kind)
 
 
-def dense_gemm_swiglu(x, weight_tiled):
-    return skinny_gemm_swiglu(x, weight_tiled)
+def dense_gemm_swiglu(x, weight_tiled, activation="silu"):
+    return skinny_gemm_swiglu(x, weight_tiled, activation)
 
 
 def dense_gemm_rotary(x, wqkv, table, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim, rotary_dim, page_size, write_kv):
@@ -354,6 +420,10 @@ def sample(out, logits, temperature=None, top_k=None, top_p=None, seed=None, dra
 
 def linear(x, weight, out=None):
     return torch.matmul(x, weight.t(), out=out)
+
+
+def logits_product(x, weight):
+    return x.float() @ weight.float().t()
 
 
 class CpuPending:
@@ -393,7 +463,8 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "dense_gemm_swiglu": dense_gemm_swiglu, "dense_gemm_act": dense_gemm_act, "dense_gemm_rotary": dense_gemm_rotary,
        "sample": sample, "post_add_layernorm": post_add_layernorm, "stream_reinject": stream_reinject, "activation": activation,
        "qk_norm_rotary_store": qk_norm_rotary_store, "sigmoid_gate": sigmoid_gate, "causal_conv_silu": causal_conv_silu,
-       "conv_state_update": conv_state_update, "ssm_scan": ssm_scan, "gated_group_rmsnorm": gated_group_rmsnorm}
+       "conv_state_update": conv_state_update, "ssm_scan": ssm_scan, "gated_group_rmsnorm": gated_group_rmsnorm,
+       "add_rmsnorm_pair": add_rmsnorm_pair, "scale_softcap": scale_softcap, "latent_prep": latent_prep, "delta_rule_scan": delta_rule_scan}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered
@@ -413,6 +484,7 @@ def patched():
     with the decode products' fused epilogues)."""
     saved = {name: getattr(ops, name) for name in OPS}
     saved_linear, saved_model_linear, saved_require = gemm.linear, model_mod.linear, runner_mod._require_cuda
+    saved_logits, saved_need = gemm.logits_product, gemm._need_device
     saved_lookup, saved_mixed = graphs_mod.DecodeGraphs.lookup, graphs_mod.DecodeGraphs.lookup_mixed
     try:
         graphs_mod.DecodeGraphs.lookup = graphs_mod.DecodeGraphs.lookup_mixed = lambda self, *a, **k: None  # no captured steps without a device
@@ -420,11 +492,13 @@ def patched():
         for name, fn in OPS.items():
             setattr(ops, name, _counted(name, fn))
         gemm.linear = model_mod.linear = linear
+        gemm.logits_product, gemm._need_device = logits_product, lambda x, what: None
         runner_mod._require_cuda = lambda device: None
         yield
     finally:
         for name, fn in saved.items():
             setattr(ops, name, fn)
         gemm.linear, model_mod.linear, runner_mod._require_cuda = saved_linear, saved_model_linear, saved_require
+        gemm.logits_product, gemm._need_device = saved_logits, saved_need
         graphs_mod.DecodeGraphs.lookup, graphs_mod.DecodeGraphs.lookup_mixed = saved_lookup, saved_mixed
 

@@ -63,7 +63,7 @@ MUTANTS = {
     "the mixer's output is not added": (block_mod.PreNormBlock, "forward", "normed_input(self.ffn_norm, stream.h, a, self.ffn)", "normed_input(self.ffn_norm, stream.h, None, self.ffn)"),
     "every layer writes into the first layer's cache": (model_mod.DecoderModel, "forward", "forward(stream, batch, caches[i])", "forward(stream, batch, caches[0])"),
     "the last layer's output misses the final norm": (model_mod.DecoderModel, "forward", "stream.take_pending(), self.head, rows=rows)", "None, self.head, rows=rows)"),
-    "gate and up change places": (mlp_mod.SwiGLU, "load", 'gate, up = tensors[px + "gate_proj.weight"], tensors[px + "up_proj.weight"]', 'up, gate = tensors[px + "gate_proj.weight"], tensors[px + "up_proj.weight"]'),
+    "gate and up change places": (mlp_mod.SwiGLU, "load", 'gate, up = tensors[self.names["gate"]], tensors[self.names["up"]]', 'up, gate = tensors[self.names["gate"]], tensors[self.names["up"]]'),
     "keys and values change places at load": (GQAttention, "load", 'tensors[px + "k_proj.weight"], tensors[px + "v_proj.weight"]], 0)', 'tensors[px + "v_proj.weight"], tensors[px + "k_proj.weight"]], 0)'),
     "the scale of the scores is lost": (GQAttention, "forward", "self.nh, self.scale, self.window,", "self.nh, 1.0, self.window,"),
     "a pending product is dropped instead of computed": (ResidualStream, "take_pending", "return self._pending", "return None if type(self._pending).__name__ == 'PendingProduct' else self._pending"),
