@@ -1,5 +1,6 @@
 // What lies between an attention mixer's projections and its attention kernel when queries and keys are
-// normed over their whole projection, and what lies behind the attention kernel when its output is gated.
+// normed over their whole projection, or when the keys and values are one cached latent; and what lies behind the
+// attention kernel when its output is gated.
 // float32 and bfloat16 instantiations; all arithmetic is float32.
 #include "common.cuh"
 
@@ -248,6 +249,77 @@ DLI_EXPORT int dli_qk_norm_rotary_store(void* q_out, const void* proj, long long
                    (const __nv_bfloat16*)proj, proj_stride, wq, wk, eps, positions, inv_freq, slots, (__nv_bfloat16*)k_pool,
                    (__nv_bfloat16*)v_pool, nh, nkv, d, rot, page_size, write_kv, normed, values_from_keys);
   }
+  return (int)e;
+}
+
+// ---------------------------------------------------------------- attention over a cached latent
+// One block per token.  proj row: per head d plain and dr rotated query numbers (nh heads), then the down projection:
+// r latent numbers and dr numbers of a key part that all heads share.
+//   latent <- latent / rms(latent) * w_norm                      (float32; eps inside the root)
+//   the first `rot` of the dr numbers of the key part and of every head's query part are rotated by the position
+//   (rotate-half pairing, angle float32(position) * inv_freq[i]); the rest pass through
+//   cache row  latent | key part      -> k_pool [pages][1][page_size][r + dr] at the token's slot (if slots)
+//   query parts                       -> q_out [n][nh][r + dr], columns r .. r + dr of every head
+template <typename T>
+__global__ void latent_prep_kernel(T* __restrict__ q_out, const T* __restrict__ proj, long long proj_stride,
+                                   const float* __restrict__ w_norm, float eps, const int* __restrict__ positions,
+                                   const float* __restrict__ inv_freq, const int* __restrict__ slots, T* __restrict__ k_pool, int nh,
+                                   int d, int dr, int r, int rot, int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float trig[];  // cos[half] | sin[half]
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int half = rot >> 1;
+  const T* src = proj + (size_t)t * proj_stride;
+  const T* down = src + (size_t)nh * (d + dr);
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < r; i += blockDim.x) {
+    const float x = to_float(down[i]);
+    ss = fmaf(x, x, ss);
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)r + eps);  // (the barriers inside also publish trig)
+  const int slot = slots ? slots[t] : -1;
+  const int row = r + dr;
+  T* krow = slot >= 0 ? k_pool + (size_t)slot * row : nullptr;  // one KV head: a page is page_size rows back to back
+  if (krow)
+    for (int i = threadIdx.x; i < r; i += blockDim.x) krow[i] = from_float<T>(to_float(down[i]) * inv * w_norm[i]);
+  // rotated parts: head nh is the shared key part
+  for (int e = threadIdx.x; e < (nh + 1) * dr; e += blockDim.x) {
+    const int head = e / dr, i = e - head * dr;
+    const T* part = head < nh ? src + (size_t)head * (d + dr) + d : down + r;
+    float x = to_float(part[i]);
+    if (i < rot) {
+      const bool low = i < half;
+      const float other = to_float(part[low ? i + half : i - half]);
+      const float cs = trig[low ? i : i - half], sn = trig[half + (low ? i : i - half)];
+      x = low ? x * cs - other * sn : x * cs + other * sn;
+    }
+    if (head < nh) q_out[((size_t)t * nh + head) * row + r + i] = from_float<T>(x);
+    else if (krow) krow[r + i] = from_float<T>(x);
+  }
+}
+
+DLI_EXPORT int dli_latent_prep(void* q_out, const void* proj, long long proj_stride, const float* w_norm, float eps, const int* positions,
+                               const float* inv_freq, const int* slots, void* k_pool, int n, int nh, int d, int dr, int r, int rot,
+                               int page_size, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (nh < 1 || d < 1 || dr < 0 || r < 1 || rot < 0 || rot > dr || (rot & 1) || (rot && !inv_freq) || (slots && !k_pool) || page_size < 1 ||
+      rot * sizeof(float) > 48 * 1024)
+    return DLI_ERR_UNSUPPORTED;
+  const int work = r > (nh + 1) * dr ? r : (nh + 1) * dr;
+  const int threads = work >= 1024 ? 256 : 128;
+  const size_t smem = (size_t)(rot > 0 ? rot : 1) * sizeof(float);
+  cudaError_t e;
+  if (dtype == DLI_F32)
+    e = launch_pdl((latent_prep_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, (float*)q_out, (const float*)proj, proj_stride,
+                   w_norm, eps, positions, inv_freq, slots, (float*)k_pool, nh, d, dr, r, rot, page_size);
+  else
+    e = launch_pdl((latent_prep_kernel<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, 1, (__nv_bfloat16*)q_out,
+                   (const __nv_bfloat16*)proj, proj_stride, w_norm, eps, positions, inv_freq, slots, (__nv_bfloat16*)k_pool, nh, d, dr, r,
+                   rot, page_size);
   return (int)e;
 }
 

@@ -1,4 +1,4 @@
-// Paged causal attention on CUDA cores, any head size that is a multiple of 2 up to 256.
+// Paged causal attention on CUDA cores, any head size up to 1024 (a lane keeps R = 8 or 32 numbers of the output).
 // It is the float32 path's attention (true 32-bit dot products and expf) and takes any mix
 // of prompt portions and single decoded tokens: one warp per (token, query head) walks that
 // token's keys 0..position through the block table in chunks of 32, so the order of every
@@ -8,7 +8,7 @@
 
 using namespace dli;
 
-template <typename T>
+template <typename T, int R>
 __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __restrict__ q, int q_stride,
                                             const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                             const int* __restrict__ block_tables, int max_blocks,
@@ -31,9 +31,9 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
 
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   float m = -CUDART_INF_F, l = 0.f;
-  float acc[8];
+  float acc[R];
 #pragma unroll
-  for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+  for (int r = 0; r < R; ++r) acc[r] = 0.f;
 
   for (int base = lo; base <= p; base += 32) {
     const int key = base + lane;
@@ -53,14 +53,14 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
     const float corr = expf(m - m_new);  // 0 on the first chunk (m = -inf, m_new finite)
     l = l * corr + warp_sum(pj);
 #pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r] *= corr;
+    for (int r = 0; r < R; ++r) acc[r] *= corr;
     const int count = min(32, p - base + 1);
     for (int j = 0; j < count; ++j) {
       const float pb = __shfl_sync(0xffffffffu, pj, j);
       const long long vrow = __shfl_sync(0xffffffffu, row, j);
       const T* vr = v_pool + vrow;
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int r = 0; r < R; ++r) {
         const int i = lane + 32 * r;
         if (i < d) acc[r] = fmaf(pb, to_float(vr[i]), acc[r]);
       }
@@ -72,7 +72,7 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
   const float inv = 1.f / l;
   T* o = out + (size_t)t * nh * d + (size_t)h * d;
 #pragma unroll
-  for (int r = 0; r < 8; ++r) {
+  for (int r = 0; r < R; ++r) {
     const int i = lane + 32 * r;
     if (i < d) o[i] = from_float<T>(acc[r] * inv);
   }
@@ -83,18 +83,22 @@ DLI_EXPORT int dli_paged_attention_simt(void* out, const void* q, int q_stride, 
                                         const int* positions, int n, int nh, int nkv, int d, int page_size, int window,
                                         float scale, float sink, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
-  if (d < 1 || d > 256 || nkv < 1 || nh % nkv) return DLI_ERR_UNSUPPORTED;
+  if (d < 1 || d > 1024 || nkv < 1 || nh % nkv) return DLI_ERR_UNSUPPORTED;
   const int warps = 4;
   const long long total = (long long)n * nh;
   const int blocks = (int)((total + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
-  if (dtype == DLI_F32)
-    launch_pdl((paged_attention_simt_kernel<float>), dim3(blocks), dim3(warps * 32), smem, stream, 1, 
-        (float*)out, (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, block_tables, max_blocks,
-        seq_of_token, positions, n, nh, nkv, d, page_size, window, scale, sink);
-  else
-    launch_pdl((paged_attention_simt_kernel<__nv_bfloat16>), dim3(blocks), dim3(warps * 32), smem, stream, 1, 
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-        block_tables, max_blocks, seq_of_token, positions, n, nh, nkv, d, page_size, window, scale, sink);
+#define DLI_SIMT(T, R)                                                                                                                  \
+  launch_pdl((paged_attention_simt_kernel<T, R>), dim3(blocks), dim3(warps * 32), smem, stream, 1, (T*)out, (const T*)q, q_stride,       \
+             (const T*)k_pool, (const T*)v_pool, block_tables, max_blocks, seq_of_token, positions, n, nh, nkv, d, page_size, window, \
+             scale, sink)
+  if (dtype == DLI_F32) {
+    if (d <= 256) DLI_SIMT(float, 8);
+    else DLI_SIMT(float, 32);
+  } else {
+    if (d <= 256) DLI_SIMT(__nv_bfloat16, 8);
+    else DLI_SIMT(__nv_bfloat16, 32);
+  }
+#undef DLI_SIMT
   return (int)cudaGetLastError();
 }

@@ -110,6 +110,7 @@ struct DenseParams {
   __nv_bfloat16* v_pool;
   int nh, nkv, d, rot, page_size, write_kv;
   int act;        // EP_STORE: an activation on the (bfloat16-rounded) sums before they are stored: 0 none, 1 relu^2, 2 gelu-tanh, 3 silu
+                  // EP_SWIGLU: what is applied to the gate: 0 silu, 1 gelu-tanh
   int skip_tile;  // -1 in every launch of the engine: the k step whose copies a test leaves out (dli_dense_gemm_wait_test)
 };
 
@@ -187,7 +188,8 @@ __device__ __forceinline__ void epilogue_row(const DenseParams& p, uint32_t acc,
         load_chunk(acc + b * 128 + 64 + j, u, true);
         if (live) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) g[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+          for (int e = 0; e < 32; ++e)
+            g[e] = (p.act == 1 ? 0.5f * g[e] * (1.f + tanhf(0.7978845608028654f * (g[e] + 0.044715f * g[e] * g[e] * g[e]))) : g[e] / (1.f + expf(-g[e]))) * u[e];
 #pragma unroll
           for (int e = 0; e < 32; e += 8)
             if (col + e < I) store8(p.out + (size_t)row * I + col + e, g + e);
@@ -514,12 +516,13 @@ DLI_EXPORT int dli_dense_gemm_act(void* out, const void* x, const void* w, int t
   return launch_dense(p, x, w, tokens, features, K, stream);
 }
 
-// act [tokens, features / 2] = silu(gate) * up, for weights whose rows are interleaved in blocks of 64.
-DLI_EXPORT int dli_dense_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, cudaStream_t stream) {
-  if (features % 128) return DLI_ERR_UNSUPPORTED;
+// act [tokens, features / 2] = f(gate) * up (f: 0 silu, 1 gelu-tanh), for weights whose rows are interleaved in blocks of 64.
+DLI_EXPORT int dli_dense_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int gate_act, cudaStream_t stream) {
+  if (features % 128 || gate_act < 0 || gate_act > 1) return DLI_ERR_UNSUPPORTED;
   DenseParams p = {};
   p.out = (__nv_bfloat16*)act;
   p.mode = EP_SWIGLU;
+  p.act = gate_act;
   return launch_dense(p, x, w, tokens, features, K, stream);
 }
 

@@ -209,6 +209,161 @@ DLI_EXPORT int dli_add_rmsnorm(void* y, float* h, const void* delta, const float
   return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- two deltas, two norms of one stream
+// v = h[s] + (a[s] + b[s]) (either delta may be absent), y1[r] = v * rsqrt(mean(v^2) + eps) * w1 and, if y2, the same
+// with w2: the inputs of two branches that read one stream through norms of their own.  Without `rows` v goes back
+// to h.  One block a row; float32 arithmetic, one rounding per output.
+template <typename T, int THREADS, int PER_THREAD>
+__global__ void add_rmsnorm_pair_kernel(T* __restrict__ y1, T* __restrict__ y2, float* __restrict__ h, const T* __restrict__ a,
+                                        const T* __restrict__ b, const float* __restrict__ w1, const float* __restrict__ w2,
+                                        const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int s = rows ? rows[r] : r;
+  float* hrow = h + (size_t)s * H;
+  const T* arow = a ? a + (size_t)s * H : nullptr;
+  const T* brow = b ? b + (size_t)s * H : nullptr;
+  const bool any = arow || brow;
+  auto value = [&](int i) {
+    float x = hrow[i];
+    if (any) x += (arow ? to_float(arow[i]) : 0.f) + (brow ? to_float(brow[i]) : 0.f);
+    return x;
+  };
+  float v[PER_THREAD];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < PER_THREAD; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    v[k] = i < H ? value(i) : 0.f;
+    ss += v[k] * v[k];
+  }
+  // columns beyond THREADS * PER_THREAD (very wide models): streamed, computed again in pass two
+  for (int i = threadIdx.x + PER_THREAD * THREADS; i < H; i += THREADS) {
+    const float x = value(i);
+    ss += x * x;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  T* y1row = y1 + (size_t)r * H;
+  T* y2row = y2 ? y2 + (size_t)r * H : nullptr;
+#pragma unroll
+  for (int k = 0; k < PER_THREAD; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    if (i < H) {
+      if (!rows && any) hrow[i] = v[k];
+      y1row[i] = from_float<T>(v[k] * inv * w1[i]);
+      if (y2row) y2row[i] = from_float<T>(v[k] * inv * w2[i]);
+    }
+  }
+  for (int i = threadIdx.x + PER_THREAD * THREADS; i < H; i += THREADS) {
+    const float x = value(i);
+    if (!rows && any) hrow[i] = x;
+    y1row[i] = from_float<T>(x * inv * w1[i]);
+    if (y2row) y2row[i] = from_float<T>(x * inv * w2[i]);
+  }
+}
+
+// The same for H % 8 == 0 and H <= 8 * THREADS * CHUNKS, 16 and 32 bytes at a time, the row in registers.
+template <typename T, int THREADS, int CHUNKS>
+__global__ void __launch_bounds__(THREADS) add_rmsnorm_pair_vec_kernel(T* __restrict__ y1, T* __restrict__ y2, float* __restrict__ h,
+                                                                       const T* __restrict__ a, const T* __restrict__ b,
+                                                                       const float* __restrict__ w1, const float* __restrict__ w2,
+                                                                       const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int s = rows ? rows[r] : r;
+  float* hrow = h + (size_t)s * H;
+  const T* arow = a ? a + (size_t)s * H : nullptr;
+  const T* brow = b ? b + (size_t)s * H : nullptr;
+  float v[CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (threadIdx.x + c * THREADS) * 8;
+    if (col < H) {
+      load8(hrow + col, v[c]);
+      if (arow || brow) {
+        float d[8], e[8];
+        if (arow) load8(arow + col, d);
+        if (brow) load8(brow + col, e);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[c][k] += (arow ? d[k] : 0.f) + (brow ? e[k] : 0.f);
+        if (!rows) store8(hrow + col, v[c]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += v[c][k] * v[c][k];
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (threadIdx.x + c * THREADS) * 8;
+    if (col < H) {
+      float wv[8], o[8];
+      load8(w1 + col, wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = v[c][k] * inv * wv[k];
+      store8(y1 + (size_t)r * H + col, o);
+      if (y2) {
+        load8(w2 + col, wv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = v[c][k] * inv * wv[k];
+        store8(y2 + (size_t)r * H + col, o);
+      }
+    }
+  }
+}
+
+template <typename T>
+static int launch_add_rmsnorm_pair(void* y1, void* y2, float* h, const void* a, const void* b, const float* w1, const float* w2,
+                                   const int* rows, int n_rows, int H, float eps, cudaStream_t stream) {
+#define DLI_PAIR_VEC(THREADS, CHUNKS)                                                                                              \
+  return (int)launch_pdl((add_rmsnorm_pair_vec_kernel<T, THREADS, CHUNKS>), dim3(n_rows), dim3(THREADS), 0, stream, 1, (T*)y1, (T*)y2, h, \
+                         (const T*)a, (const T*)b, w1, w2, rows, H, eps)
+  const bool aligned = (((uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)h | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w1 | (uintptr_t)w2) & 15) == 0;
+  if (H % 8 == 0 && H <= 8 * 512 * 4 && aligned) {
+    if (H <= 8 * 128) DLI_PAIR_VEC(128, 1);
+    if (H <= 8 * 256) DLI_PAIR_VEC(256, 1);
+    if (H <= 8 * 256 * 2) DLI_PAIR_VEC(256, 2);
+    DLI_PAIR_VEC(512, 4);
+  }
+#undef DLI_PAIR_VEC
+  return (int)launch_pdl((add_rmsnorm_pair_kernel<T, 256, 16>), dim3(n_rows), dim3(256), 0, stream, 1, (T*)y1, (T*)y2, h, (const T*)a,
+                         (const T*)b, w1, w2, rows, H, eps);
+}
+
+DLI_EXPORT int dli_add_rmsnorm_pair(void* y1, void* y2, float* h, const void* a, const void* b, const float* w1, const float* w2,
+                                    const int* rows, int n_rows, int H, float eps, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  if (!y1 || !w1 || (y2 && !w2) || H < 1) return DLI_ERR_UNSUPPORTED;
+  return dtype == DLI_F32 ? launch_add_rmsnorm_pair<float>(y1, y2, h, a, b, w1, w2, rows, n_rows, H, eps, stream)
+                          : launch_add_rmsnorm_pair<__nv_bfloat16>(y1, y2, h, a, b, w1, w2, rows, n_rows, H, eps, stream);
+}
+
+// ---------------------------------------------------------------- logits: a factor, then a soft cap
+// x <- x * scale; if cap > 0, x <- cap * tanh(x / cap).  float32, in place.
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t total, float scale, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v * inv_cap) : v;
+  }
+}
+
+DLI_EXPORT int dli_scale_softcap(float* x, long long total, float scale, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const long long blocks = (total + threads - 1) / threads;
+  const long long most = (long long)sm_count() * 16;
+  return (int)launch_pdl(scale_softcap_kernel, dim3((unsigned)(blocks < most ? blocks : most)), dim3(threads), 0, stream, 1, x, (size_t)total,
+                         scale, cap);
+}
+
 // ---------------------------------------------------------------- rotary + cache write
 // qkv: [n, (nh + 2 nkv) * d], rows = tokens.  Query heads are rotated in place; key heads are
 // rotated and written to the key pool, value heads are copied to the value pool, at the token's
@@ -393,8 +548,14 @@ __device__ __forceinline__ void gate_up_columns(int i, int I, int tiled, int& g,
   }
 }
 
+// what a gated feed-forward applies to its gate: 0 silu, 1 gelu with the tanh approximation
+__device__ __forceinline__ float glu_activation(float g, int act) {
+  if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I, int tiled) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I, int tiled, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t total = (size_t)n * I;
@@ -405,12 +566,12 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
     gate_up_columns(i, I, tiled, gc, uc);
     const float g = to_float(gu[t * 2 * I + gc]);
     const float u = to_float(gu[t * 2 * I + uc]);
-    out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+    out[idx] = from_float<T>(glu_activation(g, act) * u);
   }
 }
 
 // bfloat16, I % 8 == 0: one 16-byte load of gate and of up, one 16-byte store, per thread
-__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I, int tiled) {
+__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I, int tiled, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.y;
@@ -427,26 +588,26 @@ __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const 
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const float2 a = __bfloat1622float2(gp[k]), b = __bfloat1622float2(up[k]);
-    rp[k] = __floats2bfloat162_rn(a.x / (1.f + expf(-a.x)) * b.x, a.y / (1.f + expf(-a.y)) * b.y);
+    rp[k] = __floats2bfloat162_rn(glu_activation(a.x, act) * b.x, glu_activation(a.y, act) * b.y);
   }
   reinterpret_cast<uint4*>(out + (size_t)t * I)[i] = r;
 }
 
-DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, int dtype, cudaStream_t stream) {
-  if (tiled && (I % 64)) return DLI_ERR_UNSUPPORTED;
+DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, int act, int dtype, cudaStream_t stream) {
+  if ((tiled && (I % 64)) || act < 0 || act > 1) return DLI_ERR_UNSUPPORTED;
   if (n == 0) return 0;
   if (dtype == DLI_BF16 && I % 8 == 0 && n <= 65535) {
     dim3 grid((I / 8 + 255) / 256, n);
-    launch_pdl((silu_mul_bf16_vec_kernel), dim3(grid), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, tiled);
+    launch_pdl((silu_mul_bf16_vec_kernel), dim3(grid), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, tiled, act);
     return (int)cudaGetLastError();
   }
   const size_t total = (size_t)n * I;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < (size_t)sm_count() * 16 ? (total + threads - 1) / threads : (size_t)sm_count() * 16);
   if (dtype == DLI_F32)
-    launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I, tiled);
+    launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I, tiled, act);
   else
-    launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I, tiled);
+    launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I, tiled, act);
   return (int)cudaGetLastError();
 }
 

@@ -133,6 +133,7 @@ struct Epilogue {
   const float* gain;
   float* out_ssq;
   int act;  // EP_STORE: an activation applied to the (bfloat16-rounded) sums before they are stored: 0 none, 1 relu^2, 2 gelu-tanh, 3 silu
+            // EP_SWIGLU: what is applied to the gate: 0 silu, 1 gelu-tanh
   const float* in_ssq;
   int in_tiles;
   float in_eps, in_inv_size;
@@ -162,7 +163,8 @@ __device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, co
     const int I = features >> 1, col = tile * 64 + fl;
     if (fl < 64 && col < I) {
       const float g = fin[fl], u = fin[fl + 64];
-      ((__nv_bfloat16*)out)[(size_t)t * I + col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+      const float a = ep.act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.f + expf(-g));
+      ((__nv_bfloat16*)out)[(size_t)t * I + col] = __float2bfloat16_rn(a * u);
     }
     return;
   }
@@ -563,13 +565,14 @@ DLI_EXPORT int dli_skinny_gemm_act(void* out, const void* x, const void* w, int 
   return launch_skinny(out, 0, x, w, tokens, features, K, slices, 0, ep, stream);
 }
 
-// act[tokens, features / 2] = silu(gate) * up, for weights whose rows are interleaved in blocks of 64
+// act[tokens, features / 2] = f(gate) * up (f: 0 silu, 1 gelu-tanh), for weights whose rows are interleaved in blocks of 64
 // (rows 128 j .. 128 j + 63: gate features 64 j .., rows 128 j + 64 .. 128 j + 127: the same up features).
-DLI_EXPORT int dli_skinny_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int slices,
+DLI_EXPORT int dli_skinny_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int slices, int gate_act,
                                       const float* in_ssq, int in_tiles, float in_eps, int in_size, cudaStream_t stream) {
-  if (features % 128) return DLI_ERR_UNSUPPORTED;
+  if (features % 128 || gate_act < 0 || gate_act > 1) return DLI_ERR_UNSUPPORTED;
   Epilogue ep = {};
   ep.mode = EP_SWIGLU;
+  ep.act = gate_act;
   if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
   return launch_skinny(act, 0, x, w, tokens, features, K, slices, 0, ep, stream);
 }

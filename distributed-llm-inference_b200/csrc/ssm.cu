@@ -383,10 +383,11 @@ store_state:
 }
 
 // out[t, part] = g / sqrt(mean(g^2 over the part) + eps) * w, g = y * silu(z); the row is cut into `parts`
-// equal runs.  z is column z_col + c of u.  One block per (token, part).
+// equal runs.  z is column z_col + c of u.  One block per (token, part).  gate_after: the gate stays out of the
+// norm, out = y / sqrt(mean(y^2) + eps) * w * silu(z).
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ u, long long u_stride,
-                                           int z_col, const float* __restrict__ w, int inner, int parts, float eps) {
+                                           int z_col, const float* __restrict__ w, int inner, int parts, float eps, int gate_after) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[33];
@@ -396,13 +397,13 @@ __global__ void gated_group_rmsnorm_kernel(T* __restrict__ out, const float* __r
   const T* zrow = u + (size_t)t * u_stride + z_col + c0;
   float q = 0.f;
   for (int i = threadIdx.x; i < size; i += blockDim.x) {
-    const float gv = yrow[i] * silu(to_float(zrow[i]));
+    const float gv = gate_after ? yrow[i] : yrow[i] * silu(to_float(zrow[i]));
     q = fmaf(gv, gv, q);
   }
   const float r = 1.f / sqrtf(block_sum(q, red) / (float)size + eps);
   for (int i = threadIdx.x; i < size; i += blockDim.x) {
-    const float gv = yrow[i] * silu(to_float(zrow[i]));
-    out[(size_t)t * inner + c0 + i] = from_float<T>(gv * r * w[c0 + i]);
+    const float gate = silu(to_float(zrow[i]));
+    out[(size_t)t * inner + c0 + i] = from_float<T>(gate_after ? yrow[i] * r * w[c0 + i] * gate : yrow[i] * gate * r * w[c0 + i]);
   }
 }
 
@@ -411,7 +412,8 @@ __global__ void gated_group_rmsnorm_kernel(T* __restrict__ out, const float* __r
 template <typename T, int THREADS, int CHUNKS>
 __global__ void __launch_bounds__(THREADS) gated_group_rmsnorm_vec_kernel(T* __restrict__ out, const float* __restrict__ y,
                                                                           const T* __restrict__ u, long long u_stride, int z_col,
-                                                                          const float* __restrict__ w, int inner, int parts, float eps) {
+                                                                          const float* __restrict__ w, int inner, int parts, float eps,
+                                                                          int gate_after) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[33];
@@ -430,8 +432,9 @@ __global__ void __launch_bounds__(THREADS) gated_group_rmsnorm_vec_kernel(T* __r
       load8(zrow + col, z);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        gv[c][k] *= silu(z[k]);
-        q = fmaf(gv[c][k], gv[c][k], q);
+        const float gate = silu(z[k]);
+        q = gate_after ? fmaf(gv[c][k], gv[c][k], q) : fmaf(gv[c][k] * gate, gv[c][k] * gate, q);
+        gv[c][k] *= gate;  // the gate is a factor of the output either way
       }
     }
   }
@@ -587,7 +590,7 @@ DLI_EXPORT int dli_ssm_scan(float* y, const void* xbc, const void* u, long long 
 }
 
 DLI_EXPORT int dli_gated_group_rmsnorm(void* out, const float* y, const void* u, long long u_stride, int z_col, const float* w, int n,
-                                       int inner, int parts, float eps, int dtype, cudaStream_t stream) {
+                                       int inner, int parts, float eps, int gate_after, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (parts < 1 || parts > 65535 || inner % parts) return DLI_ERR_UNSUPPORTED;
   const int size = inner / parts;
@@ -597,7 +600,7 @@ DLI_EXPORT int dli_gated_group_rmsnorm(void* out, const float* y, const void* u,
       (((uintptr_t)out | (uintptr_t)y | (uintptr_t)u | (uintptr_t)w) & 15) == 0) {
 #define DLI_GN_VEC(T, THREADS, CHUNKS)                                                                                               \
   return (int)launch_pdl((gated_group_rmsnorm_vec_kernel<T, THREADS, CHUNKS>), grid, dim3(THREADS), 0, stream, 1, (T*)out, y, (const T*)u, \
-                         u_stride, z_col, w, inner, parts, eps)
+                         u_stride, z_col, w, inner, parts, eps, gate_after)
 #define DLI_GN_SIZES(T)                       \
   if (size <= 256) DLI_GN_VEC(T, 32, 1);      \
   if (size <= 512) DLI_GN_VEC(T, 64, 1);      \
@@ -616,9 +619,9 @@ DLI_EXPORT int dli_gated_group_rmsnorm(void* out, const float* y, const void* u,
   const int threads = size >= 1024 ? 256 : 128;
   if (dtype == DLI_F32)
     e = launch_pdl((gated_group_rmsnorm_kernel<float>), grid, dim3(threads), 0, stream, 1, (float*)out, y, (const float*)u, u_stride, z_col, w,
-                   inner, parts, eps);
+                   inner, parts, eps, gate_after);
   else
     e = launch_pdl((gated_group_rmsnorm_kernel<__nv_bfloat16>), grid, dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, y,
-                   (const __nv_bfloat16*)u, u_stride, z_col, w, inner, parts, eps);
+                   (const __nv_bfloat16*)u, u_stride, z_col, w, inner, parts, eps, gate_after);
   return (int)e;
 }
