@@ -526,28 +526,201 @@ def design_kernels(size, pk, tokens=4096, seqs=64):
     return out
 
 
+def sugonex_sizes(width, heads, dim, rot_dim, kv_rank, window, delta_heads, delta_kv_heads, delta_dim, ff, pz, vocab=32000):
+    """A Sugonex model of eight layer runs (windowed latent attention, delta rule, latent attention with the rotated key
+    part, delta rule; the four run twice) and the Pazenex configuration of the same width, heads, feed-forward size and
+    number of layer runs (``pz``: its attention and state-space sizes)."""
+    def mlp():
+        return {"kind": "dense", "ff": ff}
+
+    win = {"type": "latent_attention_2", "mlp": mlp(),
+           "mixer": {"heads": heads, "dim": dim + rot_dim, "vdim": dim, "kv_rank": kv_rank + rot_dim, "scale": (dim + rot_dim) ** -0.5, "mask": {"size": window}}}
+    rot = {"type": "latent_attention", "mlp": mlp(),
+           "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5,
+                     "rot": {"base": 500000.0, "dims": rot_dim}}}
+    dl = {"type": "delta", "mlp": mlp(),
+          "mixer": {"heads": delta_heads, "kv_heads": delta_kv_heads, "dim": delta_dim, "vdim": delta_dim, "conv": 4}}
+    sg = {"architecture": "Sugonex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": [win, dl, rot, dl],
+          "loop": {"start": 0, "stop": 4, "times": 2}, "logit_scale": 0.5, "logit_softcap": 30.0}
+    pazenex, _ = pazenex_sizes(width=width, heads=heads, ff=ff, vocab=vocab, **pz)
+    return sg, pazenex
+
+
+# the cached row (kv_rank + rot_dim) is 128, 256 and 256 numbers: what this engine's tensor-core attention kernels take
+SUGONEX_SIZES = {
+    "w1024": dict(width=1024, heads=16, dim=64, rot_dim=32, kv_rank=96, window=1024, delta_heads=8, delta_kv_heads=4, delta_dim=128, ff=4096,
+                  pz=dict(kv_heads=4, dim=64, ssm_heads=32, state=64, groups=4)),
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, kv_rank=192, window=1024, delta_heads=16, delta_kv_heads=8, delta_dim=128, ff=8192,
+                  pz=dict(kv_heads=4, dim=128, ssm_heads=64, state=128, groups=8)),
+    "w4096": dict(width=4096, heads=32, dim=128, rot_dim=64, kv_rank=192, window=1024, delta_heads=32, delta_kv_heads=16, delta_dim=128, ff=14336,
+                  pz=dict(kv_heads=8, dim=128, ssm_heads=128, state=128, groups=8)),
+}
+
+
+def sugonex_kernels(size, pk, tokens=4096, seqs=64):
+    """Every kernel of the Sugonex parts beside the like kernel of the Pazenex (or Llama) parts, at one size: a prompt
+    portion of ``tokens`` tokens and a decode step of ``seqs`` sequences at a context of 2,048.  us, the bytes (or
+    operations) the kernel has to move, and the share of the measured HBM peak (of the CUDA cores' float32 rate for the
+    scans over a portion, of the measured bf16 rate for attention over a portion)."""
+    import torch
+
+    from dli_b200.cache.pools import LayerCache
+    from dli_b200.engine.batch import GroupView, StepBatch
+    from dli_b200.kernels import attention as attn
+    from dli_b200.kernels import gemm, ops
+
+    dev, bf = "cuda", torch.bfloat16
+    W, nh, d, dr, r, ff = size["width"], size["heads"], size["dim"], size["rot_dim"], size["kv_rank"], size["ff"]
+    Hd, Gd, dd = size["delta_heads"], size["delta_kv_heads"], size["delta_dim"]
+    pz = size["pz"]
+    row = r + dr
+    out = {}
+
+    def record(name, us, nbytes, like=None, flops=None, tensor=False):
+        rec = {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops is not None and tensor:
+            rec["tflops_bf16"] = round(flops / us / 1e6, 1)
+            rec["bf16_frac"] = round(flops / us / 1e6 / pk["bf16_tflops"], 3)
+        elif flops is not None:
+            rec["tflops_fp32"] = round(flops / us / 1e6, 2)
+            rec["simt_frac"] = round(flops / us / 1e6 / SIMT_FP32_TFLOPS, 3)
+        if like:
+            rec["like"] = like
+        out[name] = rec
+
+    def attention_batch(S, q_len, context, page=16):
+        """A batch of S sequences that each bring q_len tokens and end at ``context`` keys, in pages of their own."""
+        n = S * q_len
+        width = -(-context // page)
+        tables = torch.arange(S * width, dtype=torch.int32, device=dev).view(S, width)
+        q_start = torch.arange(S + 1, dtype=torch.int32, device=dev) * q_len
+        kv_len = torch.full((S,), context, dtype=torch.int32, device=dev)
+        seq_of = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), q_len).to(dev)
+        positions = (torch.arange(n, dtype=torch.int32) % q_len + (context - q_len)).to(dev)
+        slots = (seq_of * width * page + positions).to(torch.int32)
+        batch = StepBatch(n=n, num_seqs=S, num_single=S if q_len == 1 else 0, token_ids=positions, positions=positions, seq_of_token=seq_of,
+                          q_start=q_start, kv_len=kv_len, state_slot=torch.arange(S, dtype=torch.int32, device=dev), logit_rows=positions[:0],
+                          groups=[GroupView(tables, slots)], q_lens=[q_len] * S, starts=[context - q_len] * S, state_slots=list(range(S)),
+                          max_q_len=q_len, max_kv_len=context, max_kv_len_single=context if q_len == 1 else 0)
+        return batch, S * width
+
+    for label, n, S in (("portion", tokens, 1), ("decode", seqs, seqs)):
+        q_len = n // S
+        context = tokens if S == 1 else 2048
+        q_start = torch.arange(S + 1, dtype=torch.int32, device=dev) * q_len
+        seq_of = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), q_len).to(dev)
+        slot = torch.arange(S, dtype=torch.int32, device=dev)
+        # the norm in front of both branches, with both branches' outputs of the layer before
+        h = torch.randn(n, W, device=dev)
+        a, b = torch.randn(n, W, device=dev).to(bf), torch.randn(n, W, device=dev).to(bf)
+        w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+        y1, y2 = torch.empty(n, W, dtype=bf, device=dev), torch.empty(n, W, dtype=bf, device=dev)
+        record(f"{label}.add_rmsnorm_pair", time_kernel(lambda: ops.add_rmsnorm_pair(y1, y2, h, a, b, w1, w2, 1e-6)), n * W * 16, "post_add_layernorm")
+        record(f"{label}.post_add_layernorm", time_kernel(lambda: ops.post_add_layernorm(y1, h, a, w1, w2, 1e-6, 1e-6)), n * W * 12)
+        # attention over the latent: preparation, the heads' products, the attention kernels, the gate
+        batch, pages = attention_batch(S, q_len, context)
+        pool = torch.randn(pages + 1, 1, 16, row, device=dev).to(bf)
+        cache = LayerCache(0, pool, pool, 16)
+        proj = torch.randn(n, nh * (d + dr) + row + nh * d, device=dev).to(bf)
+        q = torch.empty(n, nh * row, dtype=bf, device=dev)
+        wn = torch.ones(r, device=dev)
+        inv = (1.0 / (500000.0 ** (torch.arange(0, dr, 2).float() / dr))).to(dev)
+        slots = batch.groups[0].slots
+        record(f"{label}.latent_prep", time_kernel(lambda: ops.latent_prep(q, proj, wn, 1e-6, batch.positions, inv, slots, pool, nh, d, dr, r, dr, 16)),
+               n * ((nh * dr + row) * 4), "qk_norm_rotary_store")
+        wuk = (torch.randn(nh, d, r, device=dev) * 0.05).to(bf)
+        record(f"{label}.heads_product_uk", time_kernel(lambda: gemm.heads_product(proj[:, : nh * (d + dr)].view(n, nh, d + dr)[:, :, :d], wuk,
+                                                                                   q.view(n, nh, row)[:, :, :r])),
+               n * nh * (d + r) * 2 + nh * d * r * 2, flops=2.0 * n * nh * d * r, tensor=True)
+        lat = torch.empty(n, nh * row, dtype=bf, device=dev)
+        causal = (context * (context + 1) / 2) if S == 1 else float(context)
+        att_us = time_kernel(lambda: attn.paged_attention(lat, q, cache, batch, nh, row**-0.5, None))
+        record(f"{label}.latent_attention", att_us, S * context * row * 2 + n * nh * row * 4, "sink attention", flops=4.0 * S * causal * nh * row, tensor=True)
+        # its like: Pazenex's attention at equal heads (grouped-query, separate values)
+        pd, pkv = pz["dim"], pz["kv_heads"]
+        kp, vp = (torch.randn(pages + 1, pkv, 16, pd, device=dev).to(bf) for _ in range(2))
+        pq, po = torch.randn(n, nh * pd, device=dev).to(bf), torch.empty(n, nh * pd, dtype=bf, device=dev)
+        gqa_us = time_kernel(lambda: attn.paged_attention(po, pq, LayerCache(0, kp, vp, 16), batch, nh, pd**-0.5, None, sink=0.0))
+        record(f"{label}.sink_attention", gqa_us, S * context * pkv * pd * 4 + n * nh * pd * 4, flops=4.0 * S * causal * nh * pd, tensor=True)
+        wuv = (torch.randn(nh, r, d, device=dev) * 0.05).to(bf)
+        o = torch.empty(n, nh * d, dtype=bf, device=dev)
+        record(f"{label}.heads_product_uv", time_kernel(lambda: gemm.heads_product(lat.view(n, nh, row)[:, :, :r], wuv, o.view(n, nh, d))),
+               n * nh * (d + r) * 2 + nh * d * r * 2, flops=2.0 * n * nh * d * r, tensor=True)
+        gate = proj[:, nh * (d + dr) + row :]
+        record(f"{label}.sigmoid_gate", time_kernel(lambda: ops.sigmoid_gate(o, gate)), n * nh * d * 6)
+        # gated feed-forward's activation
+        gu = torch.randn(n, 2 * ff, device=dev).to(bf)
+        act = torch.empty(n, ff, dtype=bf, device=dev)
+        record(f"{label}.gelu_mul", time_kernel(lambda: ops.silu_mul(act, gu, True, "gelu_tanh")), n * ff * 6, "silu_mul")
+        record(f"{label}.silu_mul", time_kernel(lambda: ops.silu_mul(act, gu, True)), n * ff * 6)
+        # delta rule: convolution, scan, norm with the gate behind it
+        taps, qk, inner = 4, Gd * dd, Hd * dd
+        C = 2 * qk + inner
+        u = torch.randn(n, C + inner + 2 * Hd, device=dev).to(bf)
+        qkv = torch.empty(n, C, dtype=bf, device=dev)
+        cw = torch.randn(taps, C, device=dev)
+        cstate = torch.zeros(S, taps - 1, C, dtype=bf, device=dev)
+        record(f"{label}.causal_conv_silu", time_kernel(lambda: ops.causal_conv_silu(qkv, u, 0, cw, None, cstate, seq_of, q_start, slot)),
+               n * C * 4 + (S * (taps - 1) * C * 2 if S > 1 else 0))
+        state = torch.zeros(S, Hd, dd, dd, device=dev)
+        os_ = torch.empty(n, inner, device=dev)
+        dtb, al = torch.zeros(Hd, device=dev), torch.full((Hd,), -3.0, device=dev)
+        scan_us = time_kernel(lambda: ops.delta_rule_scan(os_, qkv, u, C + inner, C + inner + Hd, dtb, al, state, q_start, slot, Gd, dd, 1e-6, max_len=q_len))
+        record(f"{label}.delta_rule_scan", scan_us, S * Hd * dd * dd * 8 + n * (C * 2 + inner * 4), "ssm_scan", flops=8.0 * n * Hd * dd * dd)
+        # its like: the state-space scan of the Pazenex model of this size
+        Hs, P, N, G = pz["ssm_heads"], 64, pz["state"], pz["groups"]
+        sin, sC = Hs * P, Hs * P + 2 * G * N
+        su = torch.randn(n, sin + sC + Hs, device=dev).to(bf)
+        xbc = torch.randn(n, sC, device=dev).to(bf)
+        sstate = torch.zeros(S, Hs, P, N, device=dev)
+        ys = torch.empty(n, sin, device=dev)
+        z3 = torch.zeros(Hs, device=dev)
+        ssm_us = time_kernel(lambda: ops.ssm_scan(ys, xbc, su, sin + sC, z3, z3, z3 + 1, sstate, q_start, slot, G, max_len=q_len))
+        record(f"{label}.ssm_scan", ssm_us, S * Hs * N * P * 8 + n * (sC * 2 + sin * 4), flops=5.0 * n * Hs * N * P)
+        gated = torch.empty(n, inner, dtype=bf, device=dev)
+        nw = torch.ones(inner, device=dev)
+        record(f"{label}.group_norm_gate_after", time_kernel(lambda: ops.gated_group_rmsnorm(gated, os_, u, C, nw, Hd, 1e-6, gate_after=True)), n * inner * 8,
+               "gated_group_rmsnorm")
+        record(f"{label}.gated_group_rmsnorm", time_kernel(lambda: ops.gated_group_rmsnorm(gated, os_, u, C, nw, Hd, 1e-6)), n * inner * 8)
+    logits = torch.randn(seqs, 32000, device=dev)
+    record("decode.scale_softcap", time_kernel(lambda: ops.scale_softcap(logits, 0.5, 30.0)), seqs * 32000 * 8)
+    return out
+
+
 SIMT_FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12  # CUDA-core multiply-adds of a B200 at 1.9 GHz: the scan's ceiling (no float32 tensor-core path)
 
 
+DESIGNS = {
+    # design -> (sizes by name, what builds the two configurations of a size, the closest existing model, the kernels' table)
+    "pazenex": (DESIGN_SIZES, pazenex_sizes, "llama", design_kernels),
+    "sugonex": (SUGONEX_SIZES, sugonex_sizes, "pazenex", sugonex_kernels),
+}
+
+
 def design_arm(args) -> int:
-    """``--design pazenex``: prefill and decode throughput of Pazenex models with random weights at layer sizes that resemble
-    real models, beside Llama models of the same width, heads, feed-forward size and number of layer runs; and every
-    kernel of the new parts beside its like among the Llama parts."""
+    """``--design NAME``: prefill and decode throughput of models of that architecture with random weights at layer sizes
+    that resemble real models, beside the closest existing architecture at the same width, heads, feed-forward size and
+    number of layer runs; and every kernel of the new parts beside its like among the other model's parts."""
     import torch
 
     import dli_b200
 
+    sizes, build, other, kernels = DESIGNS[args.design]
     pk = peaks()
-    line = {"design": args.design, "dtype": "bf16", "data": "synthetic: uniform-random token ids, seeded random weights", "sizes": {},
+    line = {"design": args.design, "beside": other, "dtype": "bf16", "data": "synthetic: uniform-random token ids, seeded random weights", "sizes": {},
             "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "simt_fp32_tflops": round(SIMT_FP32_TFLOPS, 1), "source": pk["source"]}}
-    names = [args.size] if args.size else list(DESIGN_SIZES)
+    names = [args.size] if args.size else list(sizes)
     for name in names:
-        pz_cfg, llama_cfg = pazenex_sizes(**DESIGN_SIZES[name])
+        new_cfg, other_cfg = build(**sizes[name])
+        # the matrix products' share of a prefill, counted on the Llama shape of these sizes
+        flops_cfg = dict(LLAMA_3_2_1B, hidden_size=sizes[name]["width"], num_attention_heads=sizes[name]["heads"],
+                         num_key_value_heads=sizes[name].get("kv_heads", sizes[name]["heads"]), head_dim=sizes[name]["dim"],
+                         intermediate_size=sizes[name]["ff"], vocab_size=32000)
         rec = {}
-        for label, cfg in (("pazenex", pz_cfg), ("llama", llama_cfg)):
+        for label, cfg in ((args.design, new_cfg), (other, other_cfg)):
             model = dli_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
             wbytes = all_weight_bytes(model)
-            prefill = prefill_timed(model, llama_cfg, 8, pk["bf16_tflops"], reps=3, warmup=3, tokens=args.prompt_len)
+            prefill = prefill_timed(model, flops_cfg, 8, pk["bf16_tflops"], reps=3, warmup=3, tokens=args.prompt_len)
             decode = decode_device_timed(model, args.batch, args.steps, args.warmup, blocks=1, prompt_len=args.prompt_len,
                                          context=args.prompt_len + 512)
             rec[label] = {"prefill_tok_s": round(prefill["value"], 1), "prefill_ms": round(prefill["ms"], 3),
@@ -557,7 +730,7 @@ def design_arm(args) -> int:
             torch.cuda.empty_cache()
         line["sizes"][name] = rec
     if not args.skip_points:
-        line["kernels"] = design_kernels(DESIGN_SIZES[args.size or "w2048"], pk)
+        line["kernels"] = kernels(sizes[args.size or "w2048"], pk)
     print(json.dumps(line))
     return 0
 
@@ -762,9 +935,9 @@ def main() -> int:
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "sample"],
                     help="profiling runs: only the device-timed decode steps, only the prefill step, or only the sampling kernel (prints a short line)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the step's kernels one by one")
-    ap.add_argument("--design", default=None, choices=["pazenex"],
+    ap.add_argument("--design", default=None, choices=["pazenex", "sugonex"],
                     help="another measurement: this architecture beside Llama at equal sizes, and its kernels beside their likes (prints its own line)")
-    ap.add_argument("--size", default=None, choices=list(DESIGN_SIZES), help="--design: one size only")
+    ap.add_argument("--size", default=None, choices=list(DESIGN_SIZES), help="--design: one size only (every design has these names)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="profiling runs: the context at which decoding starts (--phase decode), the prompt's length (--phase prefill)")
     args = ap.parse_args()
