@@ -286,19 +286,21 @@ __global__ void latent_prep_kernel(T* __restrict__ q_out, const T* __restrict__ 
   T* krow = slot >= 0 ? k_pool + (size_t)slot * row : nullptr;  // one KV head: a page is page_size rows back to back
   if (krow)
     for (int i = threadIdx.x; i < r; i += blockDim.x) krow[i] = from_float<T>(to_float(down[i]) * inv * w_norm[i]);
-  // rotated parts: head nh is the shared key part
-  for (int e = threadIdx.x; e < (nh + 1) * dr; e += blockDim.x) {
-    const int head = e / dr, i = e - head * dr;
+  // rotated parts, a pair of partners (i, i + half) a thread: head nh is the shared key part
+  const int pairs = half + (dr - rot);  // per head: the rotated pairs, then the numbers that pass through
+  for (int e = threadIdx.x; e < (nh + 1) * pairs; e += blockDim.x) {
+    const int head = e / pairs, j = e - head * pairs;
     const T* part = head < nh ? src + (size_t)head * (d + dr) + d : down + r;
-    float x = to_float(part[i]);
-    if (i < rot) {
-      const bool low = i < half;
-      const float other = to_float(part[low ? i + half : i - half]);
-      const float cs = trig[low ? i : i - half], sn = trig[half + (low ? i : i - half)];
-      x = low ? x * cs - other * sn : x * cs + other * sn;
+    T* dst = head < nh ? q_out + ((size_t)t * nh + head) * row + r : (krow ? krow + r : nullptr);
+    if (!dst) continue;
+    if (j < half) {
+      const float lo = to_float(part[j]), hi = to_float(part[j + half]);
+      const float cs = trig[j], sn = trig[half + j];
+      dst[j] = from_float<T>(lo * cs - hi * sn);
+      dst[j + half] = from_float<T>(hi * cs + lo * sn);
+    } else {
+      dst[rot + j - half] = part[rot + j - half];
     }
-    if (head < nh) q_out[((size_t)t * nh + head) * row + r + i] = from_float<T>(x);
-    else if (krow) krow[r + i] = from_float<T>(x);
   }
 }
 
@@ -310,7 +312,7 @@ DLI_EXPORT int dli_latent_prep(void* q_out, const void* proj, long long proj_str
       rot * sizeof(float) > 48 * 1024)
     return DLI_ERR_UNSUPPORTED;
   const int work = r > (nh + 1) * dr ? r : (nh + 1) * dr;
-  const int threads = work >= 1024 ? 256 : 128;
+  const int threads = work >= 4096 ? 256 : 128;  // small blocks: a token's work is short, and more blocks fit an SM
   const size_t smem = (size_t)(rot > 0 ? rot : 1) * sizeof(float);
   cudaError_t e;
   if (dtype == DLI_F32)

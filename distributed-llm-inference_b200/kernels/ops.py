@@ -1124,7 +1124,11 @@ def delta_rule_scan(o: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: 
             or u.shape[0] != n or b_col + heads > u.shape[1] or a_col + heads > u.shape[1] or d > DELTA_MAX_HEAD_DIM
             or dt_bias.numel() != heads or a_log.numel() != heads or q_start.numel() != state_slot.numel() + 1):
         raise KernelError(f"delta_rule_scan: shapes do not agree (or the head size is above {DELTA_MAX_HEAD_DIM})")
+    # the float32 rows the recurrence reads (unit vectors, values, beta, gamma, q . k), written by the first of the two kernels
+    scratch = torch.empty(n * ((2 * kv_heads * d + heads * dv + 2 * heads + kv_heads + 3) & ~3), dtype=torch.float32, device=o.device)
     f = _fn("delta_rule.cu", "dli_delta_rule_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                     c_void_p] + [c_int] * 6 + [c_float, c_int, c_void_p])
+                                                     c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_int, c_void_p])
     _check(f(_ptr(o), _ptr(qkv), _ptr(u), u.stride(0), b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(q_start), _ptr(state_slot),
-             state_slot.numel(), heads, kv_heads, d, dv, int(max_len), unit_eps, DT_CODE[u.dtype], _stream()), "delta_rule_scan")
+             _ptr(scratch), n, state_slot.numel(), heads, kv_heads, d, dv, int(max_len), unit_eps, DT_CODE[u.dtype], _stream()), "delta_rule_scan")
+    global launch_count
+    launch_count += 1  # two kernels
