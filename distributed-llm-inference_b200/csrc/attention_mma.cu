@@ -41,6 +41,7 @@ constexpr int ROW_BYTES = D * 2 + 16;   // padded row
 constexpr int TILE_BYTES = BLOCK_N * ROW_BYTES;
 constexpr int STAGES = 2;
 constexpr int SMEM_BYTES = BLOCK_M * ROW_BYTES + 2 * STAGES * TILE_BYTES;
+constexpr int SMEM_BYTES_SHARED = BLOCK_M * ROW_BYTES + STAGES * TILE_BYTES;  // one pool serves as keys and values
 
 struct Params {
   bf16* out;                 // [n, nh * D]
@@ -93,11 +94,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Copies `rows` consecutive keys (from position `base`) of one KV head into a shared-memory
-// tile, keys and values, 16 bytes per cp.async; keys outside [lo, hi) become zero rows.
+// tile, keys and values, 16 bytes per cp.async; keys outside [lo, hi) become zero rows.  SHARED: the values are read
+// from the keys' rows (one pool serves as both), so only the keys are copied and the tile serves both products.
 // `nthreads` threads take part, thread `t` of them.  When the 16-byte chunks of a row divide
 // the thread count, a thread keeps its chunk column and walks down the rows, stepping through
 // the block table without a division per copy.
-template <int ROWS>
+template <int ROWS, bool SHARED = false>
 __device__ __forceinline__ void load_kv_tile(unsigned char* dK, unsigned char* dV, const bf16* __restrict__ k_pool,
                                              const bf16* __restrict__ v_pool, const int* __restrict__ table, int base, int lo, int hi,
                                              int nkv, int kvh, int page_size, int t, int nthreads) {
@@ -112,7 +114,7 @@ __device__ __forceinline__ void load_kv_tile(unsigned char* dK, unsigned char* d
       size_t src = 0;
       if (ok) src = (((size_t)table[blk] * nkv + kvh) * page_size + off) * D + c * 8;
       cp_async16(smem_u32(dK + r * ROW_BYTES + c * 16), k_pool + src, ok ? 16 : 0);
-      cp_async16(smem_u32(dV + r * ROW_BYTES + c * 16), v_pool + src, ok ? 16 : 0);
+      if (!SHARED) cp_async16(smem_u32(dV + r * ROW_BYTES + c * 16), v_pool + src, ok ? 16 : 0);
       key += step;
       off += step;
       while (off >= page_size) { off -= page_size; ++blk; }
@@ -128,7 +130,7 @@ __device__ __forceinline__ void load_kv_tile(unsigned char* dK, unsigned char* d
         src = (((size_t)table[blk] * nkv + kvh) * page_size + (key - blk * page_size)) * D + c * 8;
       }
       cp_async16(smem_u32(dK + r * ROW_BYTES + c * 16), k_pool + src, ok ? 16 : 0);
-      cp_async16(smem_u32(dV + r * ROW_BYTES + c * 16), v_pool + src, ok ? 16 : 0);
+      if (!SHARED) cp_async16(smem_u32(dV + r * ROW_BYTES + c * 16), v_pool + src, ok ? 16 : 0);
     }
   }
 }
@@ -221,13 +223,14 @@ __device__ __forceinline__ void tile_update(const unsigned char* sQ, const unsig
   }
 }
 
+template <bool SHARED>
 __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Params p) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sQ = smem;
   unsigned char* sK = smem + BLOCK_M * ROW_BYTES;
-  unsigned char* sV = sK + STAGES * TILE_BYTES;
+  unsigned char* sV = SHARED ? sK : sK + STAGES * TILE_BYTES;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int s = p.seq0 + blockIdx.y;
@@ -267,8 +270,8 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Para
   }
 
   auto load_tile = [&](int stage, int t) {
-    load_kv_tile<BLOCK_N>(sK + stage * TILE_BYTES, sV + stage * TILE_BYTES, p.k_pool, p.v_pool, table, t * BLOCK_N, lo, hi, p.nkv, kvh,
-                          p.page_size, tid, THREADS);
+    load_kv_tile<BLOCK_N, SHARED>(sK + stage * TILE_BYTES, sV + stage * TILE_BYTES, p.k_pool, p.v_pool, table, t * BLOCK_N, lo, hi, p.nkv, kvh,
+                                  p.page_size, tid, THREADS);
   };
 
 
@@ -349,17 +352,20 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Para
 // throughput, so occupancy decides: with many (sequence, KV head) pairs small tiles and a
 // short pipeline leave room for five CTAs per SM; with few pairs a deeper pipeline of larger
 // tiles keeps more bytes in flight per CTA.
-template <int KEYS, int PIPE>
+template <int KEYS, int PIPE, bool ONE_POOL = false>
 struct DecodeShape {
   static constexpr int N = KEYS;                      // keys per tile of one warp
   static constexpr int STAGES = PIPE;
+  static constexpr bool SHARED = ONE_POOL;            // the values are read from the keys' rows: no value stages
   static constexpr int TILE = KEYS * ROW_BYTES;
-  static constexpr int WARP = 2 * PIPE * TILE;        // K and V stages of one warp
+  static constexpr int WARP = (ONE_POOL ? 1 : 2) * PIPE * TILE;  // K and V stages of one warp
   static constexpr int MERGE = NWARPS * 16 * (D + 2) * 4;  // per warp: o[16][D], m[16], l[16]
   static constexpr int SMEM = 16 * ROW_BYTES + (NWARPS * WARP > MERGE ? NWARPS * WARP : MERGE);
 };
 typedef DecodeShape<16, 2> DecodeMany;
 typedef DecodeShape<(D <= 128 ? 32 : 16), (D <= 64 ? 3 : 2)> DecodeFew;
+typedef DecodeShape<16, 2, true> DecodeManyShared;
+typedef DecodeShape<(D <= 128 ? 32 : 16), (D <= 128 ? 3 : 2), true> DecodeFewShared;
 
 // grid (splits, sequences, kv heads * chunks of 16 query heads); every sequence brings one token.
 template <typename Shape>
@@ -401,10 +407,10 @@ __global__ void __launch_bounds__(THREADS) paged_decode_mma_kernel(const Params 
   __syncthreads();
 
   unsigned char* wK = sKV + warp * DEC_WARP_BYTES;
-  unsigned char* wV = wK + DEC_STAGES * DEC_TILE_BYTES;
+  unsigned char* wV = Shape::SHARED ? wK : wK + DEC_STAGES * DEC_TILE_BYTES;
   auto load_tile = [&](int stage, int t) {
-    load_kv_tile<DEC_N>(wK + stage * DEC_TILE_BYTES, wV + stage * DEC_TILE_BYTES, p.k_pool, p.v_pool, table, t * DEC_N, lo, hi, p.nkv,
-                        kvh, p.page_size, lane, 32);
+    load_kv_tile<DEC_N, Shape::SHARED>(wK + stage * DEC_TILE_BYTES, wV + stage * DEC_TILE_BYTES, p.k_pool, p.v_pool, table, t * DEC_N, lo, hi, p.nkv,
+                                       kvh, p.page_size, lane, 32);
   };
 
 
@@ -525,7 +531,13 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
   if (nkv < 1 || nh % nkv || splits < 1 || (splits > 1 && (max_q_len != 1 || !part_acc || !part_ml))) return DLI_ERR_UNSUPPORTED;
   static OncePerDevice configured;
   if (!configured.here()) {
-    cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(paged_attention_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_SHARED);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(paged_decode_mma_kernel<DecodeManyShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeManyShared::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(paged_decode_mma_kernel<DecodeFewShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeFewShared::SMEM);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(paged_decode_mma_kernel<DecodeMany>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeMany::SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -545,16 +557,25 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
   p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
   p.tokens_per_tile = BLOCK_M / p.heads_per_chunk;
   p.splits = splits; p.part_acc = part_acc; p.part_ml = part_ml;
+  const bool one_pool = k_pool == v_pool;  // the values lie in the keys' rows: a tile is copied once and serves both products
   if (max_q_len == 1) {
     const dim3 grid(splits, num_seqs, nkv * ((G + 15) / 16));
-    if ((long long)num_seqs * grid.z >= 2 * sm_count())
+    const bool many = (long long)num_seqs * grid.z >= 2 * sm_count();
+    if (many && one_pool)
+      launch_pdl((paged_decode_mma_kernel<DecodeManyShared>), grid, dim3(THREADS), DecodeManyShared::SMEM, stream, 1, p);
+    else if (many)
       launch_pdl((paged_decode_mma_kernel<DecodeMany>), grid, dim3(THREADS), DecodeMany::SMEM, stream, 1, p);
+    else if (one_pool)
+      launch_pdl((paged_decode_mma_kernel<DecodeFewShared>), grid, dim3(THREADS), DecodeFewShared::SMEM, stream, 1, p);
     else
       launch_pdl((paged_decode_mma_kernel<DecodeFew>), grid, dim3(THREADS), DecodeFew::SMEM, stream, 1, p);
   } else {
     const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
     dim3 grid(tiles * splits, num_seqs, nkv * p.head_chunks);
-    launch_pdl((paged_attention_mma_kernel), dim3(grid), dim3(THREADS), SMEM_BYTES, stream, 1, p);
+    if (one_pool)
+      launch_pdl((paged_attention_mma_kernel<true>), dim3(grid), dim3(THREADS), SMEM_BYTES_SHARED, stream, 1, p);
+    else
+      launch_pdl((paged_attention_mma_kernel<false>), dim3(grid), dim3(THREADS), SMEM_BYTES, stream, 1, p);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
