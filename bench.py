@@ -665,7 +665,7 @@ def sugonex_kernels(size, pk, tokens=4096, seqs=64):
         state = torch.zeros(S, Hd, dd, dd, device=dev)
         os_ = torch.empty(n, inner, device=dev)
         dtb, al = torch.zeros(Hd, device=dev), torch.full((Hd,), -3.0, device=dev)
-        scan_us = time_kernel(lambda: ops.delta_rule_scan(os_, qkv, u, C + inner, C + inner + Hd, dtb, al, state, q_start, slot, Gd, dd, 1e-6, max_len=q_len))
+        scan_us = time_kernel(lambda: ops.delta_rule_scan(os_, qkv, u, C + inner, C + inner + Hd, dtb, al, state, seq_of, q_start, slot, Gd, dd, 1e-6, max_len=q_len))
         record(f"{label}.delta_rule_scan", scan_us, S * Hd * dd * dd * 8 + n * (C * 2 + inner * 4), "ssm_scan", flops=8.0 * n * Hd * dd * dd)
         # its like: the state-space scan of the Pazenex model of this size
         Hs, P, N, G = pz["ssm_heads"], 64, pz["state"], pz["groups"]

@@ -1107,8 +1107,8 @@ DELTA_MAX_HEAD_DIM = 256
 
 
 def delta_rule_scan(o: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: int, a_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
-                    state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, kv_heads: int, head_dim: int, unit_eps: float,
-                    max_len: int = 1 << 30) -> None:
+                    state: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, kv_heads: int, head_dim: int,
+                    unit_eps: float, max_len: int = 1 << 30) -> None:
     """The gated delta rule over every sequence's tokens of this step, from and to its slot of ``state``
     [slots, heads, dv, d] (float32; S transposed, so that a value column's d numbers are contiguous).
     qkv [n, 2 kv_heads d + heads dv] holds q | k | v after convolution and activation; b and a are columns b_col + head and
@@ -1117,18 +1117,21 @@ def delta_rule_scan(o: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: 
     S <- gamma S, w = beta (v - S^T k), S <- S + k w^T, o = S^T q.  o [n, heads dv] float32."""
     _columns(u, "delta_rule_scan"), _need(qkv, "qkv", u.dtype), _need(o, "o", torch.float32), _need(state, "state", torch.float32)
     _need(dt_bias, "dt_bias", torch.float32), _need(a_log, "a_log", torch.float32)
-    _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32), _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
     _, heads, dv, d = state.shape
     n = qkv.shape[0]
     if (d != head_dim or kv_heads < 1 or heads % kv_heads or qkv.shape[1] != 2 * kv_heads * d + heads * dv or tuple(o.shape) != (n, heads * dv)
-            or u.shape[0] != n or b_col + heads > u.shape[1] or a_col + heads > u.shape[1] or d > DELTA_MAX_HEAD_DIM
+            or u.shape[0] != n or b_col + heads > u.shape[1] or a_col + heads > u.shape[1] or d > DELTA_MAX_HEAD_DIM or seq_of_token.numel() != n
             or dt_bias.numel() != heads or a_log.numel() != heads or q_start.numel() != state_slot.numel() + 1):
         raise KernelError(f"delta_rule_scan: shapes do not agree (or the head size is above {DELTA_MAX_HEAD_DIM})")
-    # the float32 rows the recurrence reads (unit vectors, values, beta, gamma, q . k), written by the first of the two kernels
-    scratch = torch.empty(n * ((2 * kv_heads * d + heads * dv + 2 * heads + kv_heads + 3) & ~3), dtype=torch.float32, device=o.device)
+    # the float32 rows the recurrence reads, written by the first two of the three kernels: unit vectors, values, four numbers a
+    # head, and every token's coefficients with the tokens of its tile of 16 (csrc/delta_rule.cu: row_layout)
+    stride = ((2 * kv_heads * d + heads * dv + 3) & ~3) + 4 * heads + 2 * heads * 16
+    scratch = torch.empty(n * stride, dtype=torch.float32, device=o.device)
     f = _fn("delta_rule.cu", "dli_delta_rule_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                     c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_int, c_void_p])
-    _check(f(_ptr(o), _ptr(qkv), _ptr(u), u.stride(0), b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(q_start), _ptr(state_slot),
-             _ptr(scratch), n, state_slot.numel(), heads, kv_heads, d, dv, int(max_len), unit_eps, DT_CODE[u.dtype], _stream()), "delta_rule_scan")
+                                                     c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_int, c_void_p])
+    _check(f(_ptr(o), _ptr(qkv), _ptr(u), u.stride(0), b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(seq_of_token), _ptr(q_start),
+             _ptr(state_slot), _ptr(scratch), n, state_slot.numel(), heads, kv_heads, d, dv, int(max_len), unit_eps, DT_CODE[u.dtype], _stream()),
+           "delta_rule_scan")
     global launch_count
-    launch_count += 1  # two kernels
+    launch_count += 2  # three kernels

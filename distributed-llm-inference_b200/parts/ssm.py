@@ -168,7 +168,7 @@ class GatedDeltaRule(Part):
         if self.taps > 1:
             ops.conv_state_update(conv_state, u, 0, batch.q_start, batch.state_slot)
         o = torch.empty((n, self.inner), dtype=torch.float32, device=x.device)
-        ops.delta_rule_scan(o, qkv, u, self.b_col, self.a_col, w["dt_bias"], w["A_log"], state, batch.q_start, batch.state_slot,
+        ops.delta_rule_scan(o, qkv, u, self.b_col, self.a_col, w["dt_bias"], w["A_log"], state, batch.seq_of_token, batch.q_start, batch.state_slot,
                             self.kv_heads, self.d, self.unit_eps, max_len=batch.max_q_len)
         gated = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         ops.gated_group_rmsnorm(gated, o, u, self.g_col, w["norm"], self.heads, self.eps, gate_after=True)

@@ -300,7 +300,7 @@ def gated_group_rmsnorm(out, y, u, z_col, weight, parts, eps, gate_after=False):
     out.copy_((g.view(n, inner) * weight * (gate if gate_after else 1.0)).to(out.dtype))
 
 
-def delta_rule_scan(o, qkv, u, b_col, a_col, dt_bias, a_log, state, q_start, state_slot, kv_heads, head_dim, unit_eps, max_len=0):
+def delta_rule_scan(o, qkv, u, b_col, a_col, dt_bias, a_log, state, seq_of_token, q_start, state_slot, kv_heads, head_dim, unit_eps, max_len=0):
     _, heads, dv, d = state.shape  # the state is kept transposed: [slot, head, value column, key row]
     qk = kv_heads * d
     fan = heads // kv_heads

@@ -123,9 +123,10 @@ def test_delta_rule_scan(dtype, tol, heads, kv_heads, d, dv):
     state = _rand(slots, heads, dv, d, seed=5) * 0.5
     s_ref, s_dev = state.clone(), state.cuda()
     o_ref, o_dev = torch.zeros(n, heads * dv), torch.zeros(n, heads * dv, device="cuda")
-    ref.delta_rule_scan(o_ref, qkv, u, 3, 3 + heads, dt_bias, a_log, s_ref, q_start, state_slot, kv_heads, d, 1e-6)
-    ops.delta_rule_scan(o_dev, qkv.cuda(), u.cuda(), 3, 3 + heads, dt_bias.cuda(), a_log.cuda(), s_dev, q_start.cuda(), state_slot.cuda(), kv_heads, d, 1e-6,
-                        max_len=max(lens))
+    seq_of = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32), torch.tensor(lens))
+    ref.delta_rule_scan(o_ref, qkv, u, 3, 3 + heads, dt_bias, a_log, s_ref, seq_of, q_start, state_slot, kv_heads, d, 1e-6)
+    ops.delta_rule_scan(o_dev, qkv.cuda(), u.cuda(), 3, 3 + heads, dt_bias.cuda(), a_log.cuda(), s_dev, seq_of.cuda(), q_start.cuda(), state_slot.cuda(),
+                        kv_heads, d, 1e-6, max_len=max(lens))
     _close(o_dev, o_ref, 1e-4, "o")  # float32 whatever the inputs' dtype
     _close(s_dev, s_ref, 1e-4, "state")
 
