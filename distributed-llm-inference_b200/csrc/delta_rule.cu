@@ -534,6 +534,7 @@ int launch_delta(float* o, const float* x32, float* state, const int* q_start, c
     if (d <= 64) return launch_tiles<4>(DLI_ARGS);
     if (d <= 128) return launch_tiles<8>(DLI_ARGS);
     if (d <= 256) return launch_tiles<16>(DLI_ARGS);
+    if (d <= 512) return launch_tiles<32>(DLI_ARGS);
   }
   // few tokens a sequence: token after token.  Threads per column: 8 hold the most state each; 16 for the largest heads.
   if (d <= 16) return launch_walk<4, 4, 16>(DLI_ARGS);
@@ -541,6 +542,7 @@ int launch_delta(float* o, const float* x32, float* state, const int* q_start, c
   if (d <= 64) return launch_walk<8, 8, 16>(DLI_ARGS);
   if (d <= 128) return launch_walk<16, 8, 16>(DLI_ARGS);
   if (d <= 256) return launch_walk<16, 16, 8>(DLI_ARGS);
+  if (d <= 512) return launch_walk<32, 16, 4>(DLI_ARGS);
 #undef DLI_ARGS
   return DLI_ERR_UNSUPPORTED;
 }
@@ -552,7 +554,7 @@ DLI_EXPORT int dli_delta_rule_scan(float* o, const void* qkv, const void* u, lon
                                    float* scratch, int n, int num_seqs, int heads, int kv_heads, int d, int dv, int max_len, float unit_eps,
                                    int dtype, cudaStream_t stream) {
   if (num_seqs == 0 || n == 0) return 0;
-  if (heads < 1 || kv_heads < 1 || heads % kv_heads || d < 1 || d > 256 || dv < 1 || num_seqs > 65535 || (dv + 7) / 8 > 65535 || !scratch)
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads || d < 1 || d > 512 || dv < 1 || num_seqs > 65535 || (dv + 7) / 8 > 65535 || !scratch)
     return DLI_ERR_UNSUPPORTED;
   const int threads = kv_heads >= 4 ? 128 : 64;
   cudaError_t e;

@@ -1103,7 +1103,7 @@ def gated_group_rmsnorm(out: torch.Tensor, y: torch.Tensor, u: torch.Tensor, z_c
 
 # ------------------------------------------------------------------ gated delta rule
 
-DELTA_MAX_HEAD_DIM = 256
+DELTA_MAX_HEAD_DIM = 512
 
 
 def delta_rule_scan(o: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: int, a_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,

@@ -109,7 +109,7 @@ def test_heads_product_into_column_slices(dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 12), (3, 3, 20, 10), (2, 1, 64, 32), (6, 2, 128, 128), (1, 1, 136, 40), (2, 2, 256, 8), (8, 4, 8, 72)])
+@pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 12), (3, 3, 20, 10), (2, 1, 64, 32), (6, 2, 128, 128), (1, 1, 136, 40), (2, 2, 256, 8), (8, 4, 8, 72), (1, 1, 320, 24), (2, 1, 512, 16)])
 def test_delta_rule_scan(dtype, tol, heads, kv_heads, d, dv):
     slots = 4
     lens = [1, 37, 0, 5, 70]  # single tokens, portions beyond one tile of tokens, an empty sequence
