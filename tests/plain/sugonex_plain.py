@@ -68,15 +68,15 @@ def softmax(s):
     return e / e.sum()
 
 
-def latent_attention(h, w, px, mix, eps):
+def latent_attention(h, w, px, mix, eps, gated):
     """Attention whose keys and values are both made from one small vector per token.
 
     W_dkv h gives kv_rank numbers, RMS-normed with a plain weight: the latent c.  If the mixer has a rotated part
     (``rot_dim``), W_dkv h has rot_dim more rows: one key part, turned by the token's position, that every head
     shares; q then holds per head ``dim`` plain numbers followed by ``rot_dim`` that are turned the same way.
     Per head the plain key is its rows of W_uk c and the value its rows of W_uv c.  Token i sees j <= i, and with
-    ``mask.size`` only the last that many (itself included).  With a tensor ``g`` the heads' outputs are multiplied
-    by sigmoid(W_g h) before W_o."""
+    ``mask.size`` only the last that many (itself included).  ``gated``: the heads' outputs are multiplied by
+    sigmoid(W_g h) before W_o."""
     T = h.shape[0]
     H, d, dv, r = mix["heads"], mix["dim"], mix["vdim"], mix["kv_rank"]
     dr = int(mix.get("rot_dim", 0) or 0)
@@ -101,7 +101,7 @@ def latent_attention(h, w, px, mix, eps):
                 s = s + k_turn[lo : i + 1] @ q_turn[i, a]
             out[i, a] = softmax(s * mix["scale"]) @ v[lo : i + 1, a]
     out = out.reshape(T, H * dv)
-    if px + "g" in w:
+    if gated:
         out = out * sigmoid(h @ w[px + "g"].T)
     return out @ w[px + "o"].T
 
@@ -153,7 +153,17 @@ def gated_feed_forward(h, w, px):
     return (gelu_tanh(h @ w[px + "gate"].T) * (h @ w[px + "up"].T)) @ w[px + "down"].T
 
 
-MIXERS = {"latent_attention": latent_attention, "latent_attention_2": latent_attention, "delta": delta_rule}
+def gated_latent_attention(h, w, px, mix, eps):
+    """The kind with a rotated key part: its output is gated."""
+    return latent_attention(h, w, px, mix, eps, gated=True)
+
+
+def windowed_latent_attention(h, w, px, mix, eps):
+    """The kind without positions: no gate."""
+    return latent_attention(h, w, px, mix, eps, gated=False)
+
+
+MIXERS = {"latent_attention": gated_latent_attention, "latent_attention_2": windowed_latent_attention, "delta": delta_rule}
 
 
 def layer_runs(cfg):

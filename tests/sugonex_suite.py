@@ -63,7 +63,7 @@ CONFIGS = {
     "no_loop": config([latent(heads=4, dim=32, rot_dim=32, vdim=32, kv_rank=96, scale=0.3), windowed(heads=4, dim=8, vdim=8, kv_rank=64, window=7),
                        delta(heads=2, kv_heads=1, dim=64, vdim=32, conv=1)], width=64, vocab=130, ff=128, no_mlp=(2,), logit_softcap=None),
     "loop_once": config([delta(), windowed(heads=1, dim=16, vdim=48, kv_rank=20, window=5)], loop=(1, 2, 1), eps=1e-6, logit_scale=None),
-    "only_latent": config([latent(), windowed(heads=5, dim=8, vdim=8, kv_rank=128, window=40)], loop=(0, 2, 2), ff=100),
+    "only_latent": config([latent(), windowed(heads=5, dim=8, vdim=8, kv_rank=128, window=36)], loop=(0, 2, 2), ff=100),
     "only_delta": config([delta(), delta(heads=6, kv_heads=3, dim=12, vdim=16, conv=2)], loop=(1, 2, 2), logit_scale=1.0, logit_softcap=None),
 }
 
