@@ -325,6 +325,82 @@ DLI_EXPORT int dli_latent_prep(void* q_out, const void* proj, long long proj_str
   return (int)e;
 }
 
+// ---------------------------------------------------------------- a product per head, for a decode step's few tokens
+// out[t, h, f] = sum_i x[t, h, i] * w[h, i, f]  (float32 sums), times sigmoid(gate[t, h, f]) if a gate is given.
+// x, out and gate are column slices of wider rows (row and head strides in elements); w [heads][in][features] is
+// contiguous.  One block per (token, head): the token's `in` numbers wait in shared memory; a thread takes a run of
+// VEC features (8 with 16-byte loads of w, else 1) and every `slices`-th row of w, so that a thread's loads are few
+// and independent of one another; the slices' partial sums meet in shared memory and are added in slice order.
+template <typename T, int VEC>
+__global__ void heads_matvec_kernel(T* __restrict__ out, long long out_row, int out_head, const T* __restrict__ x, long long x_row, int x_head,
+                                    const T* __restrict__ w, const T* __restrict__ gate, long long gate_row, int in, int features, int slices) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float hm_smem[];
+  float* xs = hm_smem;        // [in]
+  float* part = xs + in;      // [slices][features]
+  const int t = blockIdx.x, h = blockIdx.y;
+  const T* xp = x + (size_t)t * x_row + (size_t)h * x_head;
+  for (int i = threadIdx.x; i < in; i += blockDim.x) xs[i] = to_float(xp[i]);
+  __syncthreads();
+  const T* wp = w + (size_t)h * in * features;
+  const int runs = features / VEC;
+  const int run = threadIdx.x % runs, slice = threadIdx.x / runs;
+  if (slice < slices) {
+    float acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
+#pragma unroll 4
+    for (int i = slice; i < in; i += slices) {
+      const float xi = xs[i];
+      if (VEC == 8) {
+        float wv[8];
+        load8(wp + (size_t)i * features + run * 8, wv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = fmaf(xi, wv[k], acc[k]);
+      } else {
+        acc[0] = fmaf(xi, to_float(wp[(size_t)i * features + run]), acc[0]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) part[slice * features + run * VEC + k] = acc[k];
+  }
+  __syncthreads();
+  for (int f = threadIdx.x; f < features; f += blockDim.x) {
+    float v = 0.f;
+    for (int sl = 0; sl < slices; ++sl) v += part[sl * features + f];
+    if (gate) v *= 1.f / (1.f + expf(-to_float(gate[(size_t)t * gate_row + (size_t)h * features + f])));
+    out[(size_t)t * out_row + (size_t)h * out_head + f] = from_float<T>(v);
+  }
+}
+
+template <typename T>
+static int launch_heads_matvec(void* out, long long out_row, int out_head, const void* x, long long x_row, int x_head, const void* w,
+                               const void* gate, long long gate_row, int n, int heads, int in, int features, cudaStream_t stream) {
+  const int threads = 256;
+  const bool vec = (features % 8) == 0 && features / 8 <= threads && (((uintptr_t)w) & 15) == 0;
+  const int runs = vec ? features / 8 : features;
+  if (!vec && runs > threads) return DLI_ERR_UNSUPPORTED;
+  int slices = threads / runs;
+  if (slices > in) slices = in;
+  const size_t smem = (size_t)(in + slices * features) * sizeof(float);
+  if (smem > 48 * 1024) return DLI_ERR_UNSUPPORTED;
+  if (vec)
+    return (int)launch_pdl((heads_matvec_kernel<T, 8>), dim3(n, heads), dim3(threads), smem, stream, 1, (T*)out, out_row, out_head, (const T*)x, x_row,
+                           x_head, (const T*)w, (const T*)gate, gate_row, in, features, slices);
+  return (int)launch_pdl((heads_matvec_kernel<T, 1>), dim3(n, heads), dim3(threads), smem, stream, 1, (T*)out, out_row, out_head, (const T*)x, x_row,
+                         x_head, (const T*)w, (const T*)gate, gate_row, in, features, slices);
+}
+
+DLI_EXPORT int dli_heads_matvec(void* out, long long out_row, int out_head, const void* x, long long x_row, int x_head, const void* w,
+                                const void* gate, long long gate_row, int n, int heads, int in, int features, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (heads < 1 || heads > 65535 || in < 1 || features < 1) return DLI_ERR_UNSUPPORTED;
+  return dtype == DLI_F32 ? launch_heads_matvec<float>(out, out_row, out_head, x, x_row, x_head, w, gate, gate_row, n, heads, in, features, stream)
+                          : launch_heads_matvec<__nv_bfloat16>(out, out_row, out_head, x, x_row, x_head, w, gate, gate_row, n, heads, in, features,
+                                                               stream);
+}
+
 DLI_EXPORT int dli_sigmoid_gate(void* out, const void* gate, long long gate_stride, int n, int cols, int dtype, cudaStream_t stream) {
   if (n == 0 || cols == 0) return 0;
   const long long total = (long long)n * cols;

@@ -48,9 +48,12 @@ __host__ __device__ inline RowLayout row_layout(int G, int d, int H, int dv) {
 // One block per token; a warp per q/k head for the unit vectors, then all threads for v, beta and gamma.
 //   qkv [n, 2 G d + H dv]: q | k | v after convolution and activation; b and a_raw are columns b_col + head and
 //   a_col + head of u.
+// own_qk (steps that walk token after token and skip the second kernel): the token's own q . k goes to its place in
+// the token's row of Q, for every head of the q/k head.
 template <typename T>
 __global__ void delta_prep_kernel(float* __restrict__ x32, const T* __restrict__ qkv, const T* __restrict__ u, long long u_stride, int b_col,
-                                  int a_col, const float* __restrict__ dt_bias, const float* __restrict__ A_log, int H, int G, int d, int dv,
+                                  int a_col, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                  const int* __restrict__ seq_of_token, const int* __restrict__ q_start, int own_qk, int H, int G, int d, int dv,
                                   float unit_eps) {
   pdl_launch_dependents();
   pdl_wait();
@@ -64,17 +67,24 @@ __global__ void delta_prep_kernel(float* __restrict__ x32, const T* __restrict__
   for (int g = warp; g < G; g += warps) {
     const T* q = row + g * d;
     const T* k = row + G * d + g * d;
-    float sq = 0.f, sk = 0.f;
+    float sq = 0.f, sk = 0.f, qk = 0.f;
     for (int i = lane; i < d; i += 32) {
       const float qv = to_float(q[i]), kv = to_float(k[i]);
       sq = fmaf(qv, qv, sq);
       sk = fmaf(kv, kv, sk);
+      qk = fmaf(qv, kv, qk);
     }
-    sq = warp_sum(sq); sk = warp_sum(sk);
+    sq = warp_sum(sq); sk = warp_sum(sk); qk = warp_sum(qk);
     const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.f / sqrtf(sk + unit_eps);
     for (int i = lane; i < d; i += 32) {
       out[L.q + g * d + i] = to_float(q[i]) * rq;
       out[L.k + g * d + i] = to_float(k[i]) * rk;
+    }
+    if (own_qk) {
+      const int first = q_start[seq_of_token[t]];
+      const int r = t >= first ? (t - first) % TILE : 0;
+      const int fan = H / G;
+      for (int j = lane; j < fan; j += 32) out[L.qm + (g * fan + j) * TILE + r] = qk * rq * rk;
     }
   }
   for (int e = threadIdx.x; e < H * dv; e += blockDim.x) out[L.v + e] = to_float(row[2 * G * d + e]);
@@ -526,11 +536,16 @@ int launch_tiles(float* o, const float* x32, float* state, const int* q_start, c
   return launch_sized(delta_rule_tile_kernel<DPT>, set, grid, block, smem, stream, o, x32, state, q_start, state_slot, heads, kv_heads, d, dv, CB);
 }
 
+// portions go tile by tile (sizes whose float32 rows keep every copy on 16-byte boundaries); steps of few tokens a
+// sequence, and other sizes, token after token
+inline bool takes_tiles(const float* x32, int d, int dv, int max_len) {
+  return max_len > 4 && (d % 4) == 0 && (dv % 4) == 0 && (((uintptr_t)x32) & 15) == 0;
+}
+
 int launch_delta(float* o, const float* x32, float* state, const int* q_start, const int* state_slot, int num_seqs, int heads, int kv_heads, int d,
                  int dv, int max_len, cudaStream_t stream) {
 #define DLI_ARGS o, x32, state, q_start, state_slot, num_seqs, heads, kv_heads, d, dv, stream
-  // portions: tile by tile (sizes whose float32 rows keep every copy on 16-byte boundaries)
-  if (max_len > 4 && (d % 4) == 0 && (dv % 4) == 0 && (((uintptr_t)x32) & 15) == 0) {
+  if (takes_tiles(x32, d, dv, max_len)) {
     if (d <= 64) return launch_tiles<4>(DLI_ARGS);
     if (d <= 128) return launch_tiles<8>(DLI_ARGS);
     if (d <= 256) return launch_tiles<16>(DLI_ARGS);
@@ -557,14 +572,17 @@ DLI_EXPORT int dli_delta_rule_scan(float* o, const void* qkv, const void* u, lon
   if (heads < 1 || kv_heads < 1 || heads % kv_heads || d < 1 || d > 512 || dv < 1 || num_seqs > 65535 || (dv + 7) / 8 > 65535 || !scratch)
     return DLI_ERR_UNSUPPORTED;
   const int threads = kv_heads >= 4 ? 128 : 64;
+  const bool tiles = takes_tiles(scratch, d, dv, max_len);  // otherwise the walk needs of the second kernel only q . k of the token itself
   cudaError_t e;
   if (dtype == DLI_F32)
     e = launch_pdl((delta_prep_kernel<float>), dim3(n), dim3(threads), 0, stream, 1, scratch, (const float*)qkv, (const float*)u, u_stride, b_col,
-                   a_col, dt_bias, A_log, heads, kv_heads, d, dv, unit_eps);
+                   a_col, dt_bias, A_log, seq_of_token, q_start, (int)!tiles, heads, kv_heads, d, dv, unit_eps);
   else
     e = launch_pdl((delta_prep_kernel<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, 1, scratch, (const __nv_bfloat16*)qkv,
-                   (const __nv_bfloat16*)u, u_stride, b_col, a_col, dt_bias, A_log, heads, kv_heads, d, dv, unit_eps);
+                   (const __nv_bfloat16*)u, u_stride, b_col, a_col, dt_bias, A_log, seq_of_token, q_start, (int)!tiles, heads, kv_heads, d, dv,
+                   unit_eps);
   if (e != cudaSuccess) return (int)e;
+  if (!tiles) return launch_delta(o, scratch, state, q_start, state_slot, num_seqs, heads, kv_heads, d, dv, max_len, stream);
   const size_t pair_smem = (size_t)2 * kv_heads * TILE * sizeof(float);
   if (pair_smem > 48 * 1024) return DLI_ERR_UNSUPPORTED;
   e = launch_pdl(delta_pairs_kernel, dim3(n), dim3(128), pair_smem, stream, 1, scratch, seq_of_token, q_start, n, heads, kv_heads, d, dv);

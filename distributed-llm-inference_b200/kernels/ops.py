@@ -1023,6 +1023,36 @@ def latent_prep(q_out: torch.Tensor, proj: torch.Tensor, w_norm: torch.Tensor, e
              DT_CODE[proj.dtype], _stream()), "latent_prep")
 
 
+def heads_matvec_supported(in_features: int, features: int) -> bool:
+    """Sizes the small per-head product takes: a CTA of 256 threads covers the features (eight a thread when they are a
+    multiple of 8), and the token's inputs and the partial sums fit 48 KB of shared memory."""
+    runs = features // 8 if features % 8 == 0 and features // 8 <= 256 else features
+    if runs > 256:
+        return False
+    slices = min(256 // runs, in_features)
+    return (in_features + slices * features) * 4 <= 48 * 1024
+
+
+def heads_matvec(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | None = None) -> None:
+    """out[t, h, :] = x[t, h, :] @ weight[h] (float32 sums), times sigmoid(gate[t, h, :]) if given: a product per head for a
+    decode step's few tokens.  x [n, heads, in] and out [n, heads, features] may be column slices of wider rows (unit
+    stride along the last axis); weight [heads, in, features] contiguous; gate [n, heads * features], a column slice too."""
+    n, heads, feat = out.shape
+    if (x.dtype not in DT_CODE or out.dtype != x.dtype or weight.dtype != x.dtype or not (x.is_cuda and out.is_cuda and weight.is_cuda)
+            or x.shape[:2] != (n, heads) or tuple(weight.shape) != (heads, x.shape[2], feat) or not weight.is_contiguous()
+            or x.stride(2) != 1 or out.stride(2) != 1):
+        raise KernelError("heads_matvec: shapes, strides or dtypes do not agree")
+    gate_row = 0
+    if gate is not None:
+        if gate.dtype != x.dtype or tuple(gate.shape) != (n, heads * feat) or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("heads_matvec: the gate must be [n, heads * features] with unit column stride")
+        gate_row = gate.stride(0)
+    f = _fn("attention_prep.cu", "dli_heads_matvec", [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong]
+            + [c_int] * 5 + [c_void_p])
+    _check(f(c_void_p(out.data_ptr()), out.stride(0), out.stride(1), c_void_p(x.data_ptr()), x.stride(0), x.stride(1), _ptr(weight),
+             c_void_p(gate.data_ptr() if gate is not None else 0), gate_row, n, heads, x.shape[2], feat, DT_CODE[x.dtype], _stream()), "heads_matvec")
+
+
 # ------------------------------------------------------------------ state-space mixer
 
 
@@ -1134,4 +1164,4 @@ def delta_rule_scan(o: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: 
              _ptr(state_slot), _ptr(scratch), n, state_slot.numel(), heads, kv_heads, d, dv, int(max_len), unit_eps, DT_CODE[u.dtype], _stream()),
            "delta_rule_scan")
     global launch_count
-    launch_count += 2  # three kernels
+    launch_count += 2 if (max_len > 4 and d % 4 == 0 and dv % 4 == 0) else 1  # three kernels for portions, two for a decode step

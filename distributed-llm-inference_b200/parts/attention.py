@@ -232,7 +232,7 @@ class LatentAttention(Part):
         rows = [tensors[nm["q"]], tensors[nm["dkv"]]] + ([tensors[nm["g"]]] if self.gated else [])
         self.w_in = torch.cat(rows, 0).contiguous()
         self.w_uk = tensors[nm["uk"]].view(self.nh, self.d, self.rank)  # q_latent[a] = q_plain[a] W_uk[a]
-        self.w_uv = tensors[nm["uv"]].view(self.nh, self.dv, self.rank).transpose(1, 2)  # o[a] = o_latent[a] W_uv[a]^T
+        self.w_uv = tensors[nm["uv"]].view(self.nh, self.dv, self.rank).transpose(1, 2).contiguous()  # o[a] = o_latent[a] W_uv[a]^T
         self.wo, self.w_norm = tensors[nm["o"]], tensors[nm["dkv_norm"]]
 
     def cache_need(self):
@@ -254,7 +254,6 @@ class LatentAttention(Part):
         latent = torch.empty((n, self.nh * self.row), dtype=x.dtype, device=x.device)
         attn_kernels.paged_attention(latent, q, cache, batch, self.nh, self.scale, self.window, splits=batch.launch_keys.get(id(self)))
         out = torch.empty((n, self.nh * self.dv), dtype=x.dtype, device=x.device)
-        heads_product(latent.view(n, self.nh, self.row)[:, :, : self.rank], self.w_uv, out.view(n, self.nh, self.dv))
-        if self.gated:
-            ops.sigmoid_gate(out, proj[:, self.gate_col : self.gate_col + self.nh * self.dv])
+        heads_product(latent.view(n, self.nh, self.row)[:, :, : self.rank], self.w_uv, out.view(n, self.nh, self.dv),
+                      gate=proj[:, self.gate_col : self.gate_col + self.nh * self.dv] if self.gated else None)
         return project(out, self.wo)

@@ -244,6 +244,13 @@ def latent_prep(q_out, proj, w_norm, eps, positions, inv_freq, slots, k_pool, nu
         k_pool[page, 0, off, :] = torch.cat([c, turn[:, num_heads]], -1).to(k_pool.dtype)
 
 
+def heads_matvec(out, x, weight, gate=None):
+    y = torch.einsum("nhi,hif->nhf", x.float(), weight.float())
+    if gate is not None:
+        y = y * torch.sigmoid(gate.float()).view(y.shape)
+    out.copy_(y.to(out.dtype))
+
+
 def sigmoid_gate(out, gate):
     out.copy_((out.float() * torch.sigmoid(gate.float())).to(out.dtype))
 
@@ -464,7 +471,8 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "sample": sample, "post_add_layernorm": post_add_layernorm, "stream_reinject": stream_reinject, "activation": activation,
        "qk_norm_rotary_store": qk_norm_rotary_store, "sigmoid_gate": sigmoid_gate, "causal_conv_silu": causal_conv_silu,
        "conv_state_update": conv_state_update, "ssm_scan": ssm_scan, "gated_group_rmsnorm": gated_group_rmsnorm,
-       "add_rmsnorm_pair": add_rmsnorm_pair, "scale_softcap": scale_softcap, "latent_prep": latent_prep, "delta_rule_scan": delta_rule_scan}
+       "add_rmsnorm_pair": add_rmsnorm_pair, "scale_softcap": scale_softcap, "latent_prep": latent_prep, "delta_rule_scan": delta_rule_scan,
+       "heads_matvec": heads_matvec, "heads_matvec_supported": lambda in_features, features: True}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered

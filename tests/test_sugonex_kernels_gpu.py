@@ -109,6 +109,22 @@ def test_heads_product_into_column_slices(dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("n", [1, 5, 8, 40])  # the engine's own kernel up to 8 tokens, the library's batched product beyond
+def test_heads_product_with_gate(dtype, tol, n):
+    heads, d, feat, row = 3, 24, 40, 56
+    x = _rand(n, heads * row, seed=1).to(dtype)
+    w = (_rand(heads, d, feat, seed=2) * 0.3).to(dtype)
+    gate = _rand(n, heads * feat + 8, seed=3).to(dtype)
+    for g in (None, gate[:, 8:]):
+        out = torch.empty(n, heads * feat, dtype=dtype, device="cuda")
+        gemm.heads_product(x.cuda().view(n, heads, row)[:, :, 5 : 5 + d], w.cuda(), out.view(n, heads, feat), gate=None if g is None else g.cuda())
+        want = torch.einsum("nhd,hdf->nhf", x.view(n, heads, row)[:, :, 5 : 5 + d].float(), w.float())
+        if g is not None:
+            want = want * torch.sigmoid(g.float()).view(n, heads, feat)
+        _close(out.view(n, heads, feat), want, tol, f"{n} tokens, gate {g is not None}")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 12), (3, 3, 20, 10), (2, 1, 64, 32), (6, 2, 128, 128), (1, 1, 136, 40), (2, 2, 256, 8), (8, 4, 8, 72), (1, 1, 320, 24), (2, 1, 512, 16)])
 def test_delta_rule_scan(dtype, tol, heads, kv_heads, d, dv):
     slots = 4
