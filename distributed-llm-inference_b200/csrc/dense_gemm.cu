@@ -187,9 +187,13 @@ __device__ __forceinline__ void epilogue_row(const DenseParams& p, uint32_t acc,
         load_chunk(acc + b * 128 + j, g, true);
         load_chunk(acc + b * 128 + 64 + j, u, true);
         if (live) {
+          if (p.act == 1) {  // (the branch outside the loop: one of the two is compiled into each copy of it)
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            g[e] = (p.act == 1 ? 0.5f * g[e] * (1.f + tanhf(0.7978845608028654f * (g[e] + 0.044715f * g[e] * g[e] * g[e]))) : g[e] / (1.f + expf(-g[e]))) * u[e];
+            for (int e = 0; e < 32; ++e) g[e] = 0.5f * g[e] * (1.f + tanhf(0.7978845608028654f * (g[e] + 0.044715f * g[e] * g[e] * g[e]))) * u[e];
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) g[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+          }
 #pragma unroll
           for (int e = 0; e < 32; e += 8)
             if (col + e < I) store8(p.out + (size_t)row * I + col + e, g + e);

@@ -163,7 +163,9 @@ __device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, co
     const int I = features >> 1, col = tile * 64 + fl;
     if (fl < 64 && col < I) {
       const float g = fin[fl], u = fin[fl + 64];
-      const float a = ep.act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.f + expf(-g));
+      float a;
+      if (ep.act == 1) a = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+      else a = g / (1.f + expf(-g));
       ((__nv_bfloat16*)out)[(size_t)t * I + col] = __float2bfloat16_rn(a * u);
     }
     return;
