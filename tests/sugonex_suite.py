@@ -387,6 +387,22 @@ def case_the_soft_cap_bends_large_logits(tmp_path, device, dtype):
     close(Session(tmp_path / "cap", device, dtype).whole("a", toks), want, dtype, "soft cap")
 
 
+def case_layer_sizes_of_a_larger_model(tmp_path, device, dtype):
+    """Heads of 128 x 128 in the delta rule and cache rows of 128 numbers (which the TMA-fed and tcgen05 attention kernels
+    take in bfloat16, with several tiles of queries and keys), a prompt of 300 tokens in two portions, then decoding."""
+    cfg = config([windowed(heads=8, dim=64, vdim=64, kv_rank=128, scale=0.2, window=150), delta(heads=4, kv_heads=2, dim=128, vdim=128, conv=4),
+                  latent(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=0.2)], width=256, vocab=300, ff=512, loop=(0, 2, 2))
+    w = make_model(tmp_path / "big", cfg, seed=37)
+    toks = tokens_for(cfg, 320, seed=12)
+    want = plain.forward(cfg, w, toks)
+    s = Session(tmp_path / "big", device, dtype, pages=48, page_size=16)
+    rows = [0, 1, 15, 16, 127, 128, 129, 149, 150, 151, 199]
+    got = [s.step(("a", toks[:200], rows)), s.step(("a", toks[200:300], list(range(100))))]
+    got += [s.step(("a", [t], [0])) for t in toks[300:]]
+    rounding = rounding_error(tmp_path / "big", device, dtype, toks, want)
+    close(np.concatenate(got), np.concatenate([want[rows], want[200:]]), dtype, "larger sizes", rounding)
+
+
 def case_greedy_generation_through_the_engine(tmp_path, device, dtype):
     """LLMEngine.generate (scheduler, batching, sampler) against greedy decoding with the plain model."""
     from dli_b200 import LLMEngine, SamplingParams, SchedulerConfig
