@@ -55,7 +55,8 @@ def config(layers, width=48, vocab=89, ff=72, loop=None, eps=1e-5, no_mlp=(), lo
 # sizes that differ from one another in every respect: head counts, key and value sizes that differ, latents whose cache
 # row is and is not a multiple of 16, 64 and 128 (the rows the TMA-fed kernels take), partial rotation, one to four
 # taps, several value heads per q/k head and one, feed-forward sizes that are and are not a multiple of 64, loops over
-# a middle span, from the first layer, over everything, once, three times, absent; no soft cap; no logit factor
+# a middle span, from the first layer, over everything, once, three times, absent; no soft cap; no logit factor; sizes
+# that are multiples of nothing
 CONFIGS = {
     "mixed_loop": config([windowed(), delta(), latent(), delta(heads=2, kv_heads=2, dim=8, vdim=20, conv=4)], loop=(1, 3, 3)),
     "loop_from_start": config([delta(heads=3, kv_heads=1, dim=20, vdim=10, conv=2), latent(heads=2, dim=24, rot_dim=16, vdim=8, kv_rank=48, rot_dims=8)],
@@ -65,6 +66,9 @@ CONFIGS = {
     "loop_once": config([delta(), windowed(heads=1, dim=16, vdim=48, kv_rank=20, window=5)], loop=(1, 2, 1), eps=1e-6, logit_scale=None),
     "only_latent": config([latent(), windowed(heads=5, dim=8, vdim=8, kv_rank=128, window=36)], loop=(0, 2, 2), ff=100),
     "only_delta": config([delta(), delta(heads=6, kv_heads=3, dim=12, vdim=16, conv=2)], loop=(1, 2, 2), logit_scale=1.0, logit_softcap=None),
+    # nothing a multiple of 4 or 8: width, feed-forward, heads' sizes, the latent, taps beyond four
+    "odd_sizes": config([latent(heads=3, dim=7, rot_dim=6, vdim=5, kv_rank=13, rot_dims=6), delta(heads=3, kv_heads=1, dim=9, vdim=7, conv=5),
+                         windowed(heads=2, dim=5, vdim=9, kv_rank=11, window=3)], width=50, vocab=61, ff=45, loop=(1, 3, 2)),
 }
 
 
